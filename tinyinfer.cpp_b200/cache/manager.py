@@ -7,7 +7,9 @@ pool of page ids, one block table per request, and one tensor
 values), so that a page id addresses the same tokens in every layer of the group.
 Groups with different needs have pools of their own.  A group with a window gives
 a page back as soon as every position on it lies behind the window of the
-request's next token; all pages go back when the request ends.  Nothing is cleared
+request's next token, except the pages that hold the request's first ``keep_first``
+tokens, which stay readable; all pages go back when the request ends.  Values may have a
+head size of their own: a page is then a flat run of its keys followed by its values.  Nothing is cleared
 on reuse: kernels read only positions below the request's length.
 
 Beside the pages every live request holds one *state slot*, an index into
@@ -63,10 +65,16 @@ class _PagedGroup:
         return max(0, self.blocks_for(new_length) - len(self.tables.get(req, ())))
 
     def first_needed_block(self, length: int) -> int:
-        """Index of the first block the token at position ``length`` may still read."""
+        """Index of the first block behind the kept first tokens that the token at position
+        ``length`` may still read."""
         if self.spec.window is None:
             return 0
         return max(0, length - self.spec.window + 1) // self.page_size
+
+    @property
+    def kept_blocks(self) -> int:
+        """Blocks that hold a request's first ``keep_first`` tokens: never given back early."""
+        return self.blocks_for(self.spec.keep_first)
 
 
 class CacheManager:
@@ -108,9 +116,12 @@ class CacheManager:
                 s = g.spec
                 # one page more than the pool hands out: ``null_page``, where padding rows of a
                 # fixed-size (graph) batch write and read without touching a request's pages
-                g.storage = torch.zeros(
-                    (len(g.cache_slots), num_pages + 1, 2, s.num_kv_heads, page_size, s.head_dim),
-                    dtype=kv_dtype, device=device)
+                if s.v_head_dim is None or s.v_head_dim == s.head_dim:
+                    shape = (2, s.num_kv_heads, page_size, s.head_dim)
+                else:       # a page's keys [kv head][slot][head_dim], behind them its values [..][v_head_dim]
+                    shape = (s.num_kv_heads * page_size * (s.head_dim + s.v_head_dim),)
+                g.storage = torch.zeros((len(g.cache_slots), num_pages + 1, *shape),
+                                        dtype=kv_dtype, device=device)
             for slot, spec in self._state_specs.items():
                 # one slot more than requests can hold, for padding rows
                 self._state_storage[slot] = torch.zeros(
@@ -228,7 +239,7 @@ class CacheManager:
             if g.spec.window is None:
                 continue
             table = g.tables[req]
-            for b in range(min(g.first_needed_block(length), len(table))):
+            for b in range(g.kept_blocks, min(g.first_needed_block(length), len(table))):
                 if table[b] != RELEASED:
                     g.pool.give_back(table[b])
                     table[b] = RELEASED

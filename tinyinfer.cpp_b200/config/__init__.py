@@ -4,9 +4,10 @@ from .registry import (Architecture, ConfigError, architecture_of, get_architect
                        known_architectures, load_config, read_config_json,
                        register_architecture)
 from .qwen3 import Qwen3Config
+from .kagorax import KagoraxConfig
 
 __all__ = [
-    "Architecture", "ConfigError", "LayerPlan", "ModelPlan", "PartSpec", "Qwen3Config",
+    "Architecture", "ConfigError", "KagoraxConfig", "LayerPlan", "ModelPlan", "PartSpec", "Qwen3Config",
     "ScheduleEntry", "architecture_of", "default_schedule", "get_architecture",
     "known_architectures", "load_config", "read_config_json", "register_architecture",
 ]

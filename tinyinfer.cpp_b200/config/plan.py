@@ -17,7 +17,7 @@ A plan is plain data:
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Mapping, Sequence
+from typing import Any, Mapping, Optional, Sequence
 
 
 @dataclass(frozen=True)
@@ -42,9 +42,9 @@ class LayerPlan:
     """
     block: PartSpec
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: Optional[PartSpec]              # None: the layer has no feed-forward
     mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    ffn_norm: Optional[PartSpec]         # None: the block has one norm (both sublayers read it)
     names: Mapping[str, str]
 
 

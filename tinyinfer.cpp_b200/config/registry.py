@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its configuration class and plan builder.
 
-``config.json`` names its architecture in ``architectures[0]``; a GGUF file
-names it in ``general.architecture``.  Both spellings are registered for the
+``config.json`` names its architecture in ``architectures[0]`` (or in a string
+``architecture``); a GGUF file names it in ``general.architecture``.  Both spellings are registered for the
 same entry, so the model class is chosen the same way everywhere.
 """
 from __future__ import annotations
@@ -52,9 +52,12 @@ def get_architecture(name: str) -> Architecture:
 
 def architecture_of(cfg: Mapping[str, Any]) -> Architecture:
     archs = cfg.get("architectures")
-    if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json has no 'architectures' list naming the model class")
-    return get_architecture(archs[0])
+    if isinstance(archs, (list, tuple)) and archs and isinstance(archs[0], str):
+        return get_architecture(archs[0])
+    one = cfg.get("architecture")                 # some designs name their class in a plain string
+    if isinstance(one, str) and one:
+        return get_architecture(one)
+    raise ConfigError("config.json has no 'architectures' list (or 'architecture' string) naming the model class")
 
 
 def read_config_json(model_dir: str) -> dict[str, Any]:

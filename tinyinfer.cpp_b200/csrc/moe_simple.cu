@@ -1,0 +1,176 @@
+// A routed feed-forward on the CUDA cores: the router's choice, and the experts' products for
+// every operand type.
+//
+//  * router_topk: per token the `top` experts of largest logit (ties: the lower index) with the
+//    sigmoid of their logits as weights; one more column of the same product, if there is one,
+//    becomes the sigmoid gate of a shared expert.
+//  * moe_gate_up_simple: y[t][s] = silu(w g) * (w u) with g = Wgate_e h_t, u = Wup_e h_t, e and w
+//    the expert and weight of the token's slot s.  The weight stands for a scaling of the
+//    expert's input: (Wgate (w h), Wup (w h)) = (w g, w u).
+//  * moe_down_simple: out[t] += sum over the slots, in order, of Wdown_e y[t][s].
+//  * scale_rows: y[t] *= f[t].
+//
+// These are the true 32-bit kernels and the general path of the bfloat16 engine; float32
+// accumulation, k ascending inside a lane's share and a fixed butterfly across lanes, so a
+// row's bits do not depend on what else is in the batch.
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int MAX_TOP = 32;
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+__global__ void __launch_bounds__(WARPS * 32)
+router_topk_kernel(const float* logits, int stride, int num_tokens, int experts, int top,
+                   int shared_col, int* __restrict__ ids, float* __restrict__ weights,
+                   float* __restrict__ shared_gate) {
+    __shared__ int chosen[WARPS][MAX_TOP];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * WARPS + warp;
+    if (t >= num_tokens) return;
+    const float* z = logits + (size_t)t * stride;
+    for (int s = 0; s < top; ++s) {
+        float best = -INFINITY;
+        int best_e = experts;                         // larger than every index: loses every tie
+        for (int e = lane; e < experts; e += 32) {
+            bool taken = false;
+            for (int c = 0; c < s; ++c) taken |= chosen[warp][c] == e;
+            const float v = z[e];
+            if (!taken && (v > best || (v == best && e < best_e) || best_e == experts)) { best = v; best_e = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (oe < experts && (best_e == experts || ov > best || (ov == best && oe < best_e))) { best = ov; best_e = oe; }
+        }
+        if (lane == 0) {
+            chosen[warp][s] = best_e;
+            ids[(size_t)t * top + s] = best_e;
+            weights[(size_t)t * top + s] = sigmoidf_(best);
+        }
+        __syncwarp();
+    }
+    if (shared_col >= 0 && lane == 0) shared_gate[t] = sigmoidf_(z[shared_col]);
+}
+
+// one warp per output element f of one (token, slot)
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(WARPS * 32)
+moe_gate_up_simple_kernel(const TA* __restrict__ h, int h_stride, const TW* __restrict__ w_gate,
+                          const TW* __restrict__ w_up, const int* __restrict__ ids,
+                          const float* __restrict__ weights, int top, int width, int ff,
+                          TA* __restrict__ y) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ts = blockIdx.x;                        // token * top + slot
+    const int f = blockIdx.y * WARPS + warp;
+    if (f >= ff) return;
+    const int e = ids[ts];
+    const float w = weights[ts];
+    const TA* x = h + (size_t)(ts / top) * h_stride;
+    const TW* wg = w_gate + ((size_t)e * ff + f) * width;
+    const TW* wu = w_up + ((size_t)e * ff + f) * width;
+    float g = 0.0f, u = 0.0f;
+    for (int k = lane; k < width; k += 32) {
+        const float xv = to_f32(x[k]);
+        g = fmaf(xv, to_f32(wg[k]), g);
+        u = fmaf(xv, to_f32(wu[k]), u);
+    }
+    g = warp_sum(g) * w;
+    u = warp_sum(u) * w;
+    if (lane == 0) y[(size_t)ts * ff + f] = from_f32<TA>(g * sigmoidf_(g) * u);
+}
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(WARPS * 32)
+moe_down_simple_kernel(const TA* __restrict__ y, const TW* __restrict__ w_down,
+                       const int* __restrict__ ids, int top, int width, int ff,
+                       float* __restrict__ out, int out_stride) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int n = blockIdx.y * WARPS + warp;
+    if (n >= width) return;
+    float total = 0.0f;
+    for (int s = 0; s < top; ++s) {
+        const int e = ids[(size_t)t * top + s];
+        const TA* ys = y + ((size_t)t * top + s) * ff;
+        const TW* wd = w_down + ((size_t)e * width + n) * ff;
+        float acc = 0.0f;
+        for (int k = lane; k < ff; k += 32) acc = fmaf(to_f32(ys[k]), to_f32(wd[k]), acc);
+        total += warp_sum(acc);
+    }
+    if (lane == 0) out[(size_t)t * out_stride + n] += total;
+}
+
+template <typename T>
+__global__ void scale_rows_kernel(T* __restrict__ y, int stride, const float* __restrict__ f,
+                                  int rows, int cols) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * cols) return;
+    const int r = (int)(i / cols), c = (int)(i % cols);
+    T* p = y + (size_t)r * stride + c;
+    *p = from_f32<T>(to_f32(*p) * f[r]);
+}
+
+}  // namespace
+
+#define TI_DISPATCH_AW(ad, wd, CALL)                                               \
+    if (ad == TI_F32 && wd == TI_F32) { CALL(float, float); }                      \
+    else if (ad == TI_BF16 && wd == TI_BF16) { CALL(bf16, bf16); }                 \
+    else if (ad == TI_F32 && wd == TI_BF16) { CALL(float, bf16); }                 \
+    else if (ad == TI_BF16 && wd == TI_F32) { CALL(bf16, float); }                 \
+    else return ti_fail("moe: dtype codes activations=%d weights=%d are not supported", ad, wd);
+
+extern "C" int ti_router_topk(const float* logits, int stride, int num_tokens, int experts, int top,
+                              int shared_col, int* ids, float* weights, float* shared_gate,
+                              void* stream) {
+    if (num_tokens == 0) return 0;
+    TI_REQUIRE(top >= 1 && top <= MAX_TOP && top <= experts,
+               "router_topk: %d of %d experts (at most %d are chosen)", top, experts, MAX_TOP);
+    router_topk_kernel<<<(num_tokens + WARPS - 1) / WARPS, WARPS * 32, 0, (cudaStream_t)stream>>>(
+        logits, stride, num_tokens, experts, top, shared_col, ids, weights, shared_gate);
+    return ti_check_launch("router_topk");
+}
+
+extern "C" int ti_moe_gate_up_simple(const void* h, int act_dtype, int h_stride, const void* w_gate,
+                                     const void* w_up, int w_dtype, const int* ids,
+                                     const float* weights, int num_tokens, int top, int width, int ff,
+                                     void* y, void* stream) {
+    if (num_tokens == 0) return 0;
+    dim3 grid(num_tokens * top, (ff + WARPS - 1) / WARPS);
+    cudaStream_t s = (cudaStream_t)stream;
+#define CALL(TA, TW)                                                                         \
+    moe_gate_up_simple_kernel<TA, TW><<<grid, WARPS * 32, 0, s>>>(                            \
+        (const TA*)h, h_stride, (const TW*)w_gate, (const TW*)w_up, ids, weights, top, width, ff, (TA*)y)
+    TI_DISPATCH_AW(act_dtype, w_dtype, CALL)
+#undef CALL
+    return ti_check_launch("moe_gate_up_simple");
+}
+
+extern "C" int ti_moe_down_simple(const void* y, int act_dtype, const void* w_down, int w_dtype,
+                                  const int* ids, int num_tokens, int top, int width, int ff,
+                                  float* out, int out_stride, void* stream) {
+    if (num_tokens == 0) return 0;
+    dim3 grid(num_tokens, (width + WARPS - 1) / WARPS);
+    cudaStream_t s = (cudaStream_t)stream;
+#define CALL(TA, TW)                                                                         \
+    moe_down_simple_kernel<TA, TW><<<grid, WARPS * 32, 0, s>>>(                               \
+        (const TA*)y, (const TW*)w_down, ids, top, width, ff, out, out_stride)
+    TI_DISPATCH_AW(act_dtype, w_dtype, CALL)
+#undef CALL
+    return ti_check_launch("moe_down_simple");
+}
+
+extern "C" int ti_scale_rows(void* y, int dtype, int stride, const float* f, int rows, int cols,
+                             void* stream) {
+    if (rows == 0 || cols == 0) return 0;
+    const size_t n = (size_t)rows * cols;
+    const int blocks = (int)((n + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == TI_BF16) scale_rows_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)y, stride, f, rows, cols);
+    else if (dtype == TI_F32) scale_rows_kernel<float><<<blocks, 256, 0, s>>>((float*)y, stride, f, rows, cols);
+    else return ti_fail("scale_rows: dtype code %d is not supported", dtype);
+    return ti_check_launch("scale_rows");
+}

@@ -196,6 +196,15 @@ class CudaOps:
         c.ti_paged_attention_simple.argtypes = [
             _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp]
         c.ti_sample.argtypes = [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]
+        c.ti_embed_sinusoid.argtypes = [_vp, _i, _vp, _vp, _vp, _f, _i, _i, _vp, _vp]
+        c.ti_qkv_bias_norm_store.argtypes = [_vp, _i, _vp, _vp, _vp, _f, _vp, _vp, _vp, _i, _vp, _i, _i, _i,
+                                             _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp]
+        c.ti_attention_bias_simple.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
+                                               _i, _i, _i, _i, _f, _vp, _i, _vp, _i, _vp, _vp, _vp]
+        c.ti_router_topk.argtypes = [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]
+        c.ti_moe_gate_up_simple.argtypes = [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp]
+        c.ti_moe_down_simple.argtypes = [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _vp]
+        c.ti_scale_rows.argtypes = [_vp, _i, _i, _vp, _i, _i, _vp]
 
     @property
     def bf16(self):
@@ -788,6 +797,126 @@ class CudaOps:
             _code(pages, "cache"), pages.shape[0], cache.page_size, n_rows, num_heads,
             num_kv_heads, head_dim, win, float(scale), out.data_ptr(), self.status.data_ptr(),
             self._stream()))
+
+    # ---- attention with a distance bias, kept first tokens and an output gate ---------------
+    def embed_sinusoid(self, table, token_ids, positions, freq, scale, out):
+        """out[t] = float32(table[token_ids[t]]) * scale + wave(positions[t]); wave(p)[2i] =
+        sin(p freq[i]), wave(p)[2i + 1] = cos(p freq[i])."""
+        _need(out.dtype == torch.float32 and out.is_contiguous(), "embed_sinusoid: out must be float32")
+        _need(token_ids.dtype == torch.int32 and positions.dtype == torch.int32,
+              "embed_sinusoid: token ids and positions must be int32")
+        _need(freq.dtype == torch.float32 and freq.shape[0] >= (table.shape[1] + 1) // 2,
+              "embed_sinusoid: one float32 frequency per pair of columns")
+        self._ok(self.core.ti_embed_sinusoid(table.data_ptr(), _code(table, "embed_sinusoid"),
+                                             token_ids.data_ptr(), positions.data_ptr(), freq.data_ptr(),
+                                             float(scale), token_ids.shape[0], table.shape[1],
+                                             out.data_ptr(), self._stream()))
+
+    @staticmethod
+    def _page_elems(cache, num_kv_heads, dk, dv) -> int:
+        return num_kv_heads * cache.page_size * (dk + dv)
+
+    def qkv_bias_norm_store(self, proj, bias, q_weight, k_weight, eps, step, cache, q_out,
+                            num_heads, num_kv_heads, dk, dv):
+        """From the float32 product ``proj`` (columns: query heads, then, if the cache slot is
+        written, key heads and value heads; anything behind them is left alone): add ``bias``,
+        bring query and key heads to unit root mean square (times ``q_weight`` / ``k_weight`` if
+        given), store keys and values in the token's page and the queries in ``q_out``."""
+        t = proj.shape[0]
+        pages, bt = cache.pages, cache.block_table
+        writes = bool(cache.writes)
+        need = num_heads * dk + (num_kv_heads * (dk + dv) if writes else 0)
+        _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= need,
+              "qkv_bias_norm_store: the product must be float32 and hold all heads")
+        _need(bias is None or (bias.dtype == torch.float32 and bias.shape[0] >= need and bias.is_contiguous()),
+              "qkv_bias_norm_store: bias must be float32, one value per column")
+        _need(pages.is_contiguous() and pages[0].numel() == self._page_elems(cache, num_kv_heads, dk, dv),
+              "qkv_bias_norm_store: page layout")
+        _need(bt.dtype == torch.int32 and bt.stride(1) == 1, "qkv_bias_norm_store: block table int32")
+        _need(q_out.is_contiguous() and tuple(q_out.shape) == (t, num_heads * dk), "qkv_bias_norm_store: q_out")
+        self._ok(self.core.ti_qkv_bias_norm_store(
+            proj.data_ptr(), proj.stride(0), _ptr(bias), _ptr(q_weight), _ptr(k_weight), float(eps),
+            step.positions.data_ptr(), step.req_of_tok.data_ptr(), bt.data_ptr(), bt.stride(0),
+            pages.data_ptr(), _code(pages, "cache"), pages.shape[0], cache.page_size, int(writes), t,
+            num_heads, num_kv_heads, dk, dv, q_out.data_ptr(), _code(q_out, "q"),
+            self.status.data_ptr(), self._stream()))
+
+    def biased_attention(self, q, step, cache, out, num_heads, num_kv_heads, dk, dv, window, keep_first,
+                         scale, dist_bias, gate):
+        """Causal attention over the pages of each token's request: key ``j`` is visible to token
+        ``i`` when ``i - j < window`` (no window: always) or ``j < keep_first``; the score is
+        ``(q . k) * scale + dist_bias[head][min(i - j, last)]``; the normalised output is
+        multiplied by ``sigmoid(gate)`` (``gate``: float32 ``[T, heads * dv]``, rows may be strided)."""
+        pages, bt = cache.pages, cache.block_table
+        t = q.shape[0]
+        _need(q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype,
+              "biased_attention: q and out must be contiguous and of one dtype")
+        _need(tuple(q.shape) == (t, num_heads * dk) and tuple(out.shape) == (t, num_heads * dv),
+              "biased_attention: shapes of q and out")
+        _need(pages.is_contiguous() and pages[0].numel() == self._page_elems(cache, num_kv_heads, dk, dv),
+              "biased_attention: page layout")
+        _need(dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous()
+                                    and dist_bias.shape[0] == num_heads),
+              "biased_attention: the bias table must be float32 [heads, distances]")
+        _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1
+                               and tuple(gate.shape) == (t, num_heads * dv)),
+              "biased_attention: the gate must be float32 [tokens, heads * dv]")
+        self._ok(self.core.ti_attention_bias_simple(
+            q.data_ptr(), _code(q, "q"), None, step.positions.data_ptr(), step.req_of_tok.data_ptr(),
+            bt.data_ptr(), bt.stride(0), pages.data_ptr(), _code(pages, "cache"), pages.shape[0],
+            cache.page_size, t, num_heads, num_kv_heads, dk, dv, int(window or 0), int(keep_first),
+            float(scale), _ptr(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0,
+            _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(),
+            self.status.data_ptr(), self._stream()))
+
+    # ---- routed feed-forward ---------------------------------------------------------------
+    def pack_experts(self, gate, up, down):
+        """The stacked weights of a routed feed-forward (``[experts, ff, width]`` twice and
+        ``[experts, width, ff]``) in the layout the kernels want."""
+        _need(gate.dtype == up.dtype == down.dtype, "pack_experts: one dtype for all experts")
+        _code(gate, "pack_experts")
+        return {"gate": gate.contiguous(), "up": up.contiguous(), "down": down.contiguous()}
+
+    def router_topk(self, logits, experts, top, ids, weights, shared_gate=None):
+        """Per row the ``top`` largest of the first ``experts`` logits (ties: the lower index):
+        ``ids`` int32 and ``weights = sigmoid(logit)`` float32, both ``[rows, top]``; with
+        ``shared_gate`` also ``sigmoid(logits[:, experts])`` per row."""
+        t = logits.shape[0]
+        _need(logits.dtype == torch.float32 and logits.stride(1) == 1
+              and logits.shape[1] >= experts + (shared_gate is not None), "router_topk: float32 logits")
+        _need(ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.is_contiguous()
+              and weights.is_contiguous() and tuple(ids.shape) == tuple(weights.shape) == (t, top),
+              "router_topk: ids int32 and weights float32, [rows, top]")
+        self._ok(self.core.ti_router_topk(logits.data_ptr(), logits.stride(0), t, experts, top,
+                                          experts if shared_gate is not None else -1, ids.data_ptr(),
+                                          weights.data_ptr(), _ptr(shared_gate), self._stream()))
+
+    def routed_experts(self, h, w, ids, weights, residual):
+        """residual[t] += sum over slots s of Wdown_e (silu(w g) * (w u)), g = Wgate_e h[t],
+        u = Wup_e h[t], e = ids[t, s], w = weights[t, s]."""
+        t, width = h.shape
+        top = ids.shape[1]
+        experts, ff, _ = w["gate"].shape
+        _need(w["gate"].shape == w["up"].shape == (experts, ff, width) and w["down"].shape == (experts, width, ff),
+              "routed_experts: expert shapes do not agree")
+        _need(residual.dtype == torch.float32 and residual.stride(1) == 1 and tuple(residual.shape) == (t, width),
+              "routed_experts: float32 residual")
+        _need(h.stride(1) == 1, "routed_experts: rows must be contiguous")
+        y = torch.empty((t, top, ff), dtype=h.dtype, device=h.device)
+        self._ok(self.core.ti_moe_gate_up_simple(
+            h.data_ptr(), _code(h, "routed_experts"), h.stride(0), w["gate"].data_ptr(), w["up"].data_ptr(),
+            _code(w["gate"], "routed_experts"), ids.data_ptr(), weights.data_ptr(), t, top, width, ff,
+            y.data_ptr(), self._stream()))
+        self._ok(self.core.ti_moe_down_simple(
+            y.data_ptr(), _code(y, "routed_experts"), w["down"].data_ptr(), _code(w["down"], "routed_experts"),
+            ids.data_ptr(), t, top, width, ff, residual.data_ptr(), residual.stride(0), self._stream()))
+
+    def scale_rows(self, y, factors):
+        """y[r] *= factors[r] (float32 factors), in place."""
+        _need(y.stride(1) == 1 and factors.dtype == torch.float32 and factors.shape[0] == y.shape[0]
+              and factors.is_contiguous(), "scale_rows: one float32 factor per row")
+        self._ok(self.core.ti_scale_rows(y.data_ptr(), _code(y, "scale_rows"), y.stride(0), factors.data_ptr(),
+                                         y.shape[0], y.shape[1], self._stream()))
 
     # ---- sampling ------------------------------------------------------------------------
     def argmax(self, logits, out):

@@ -36,16 +36,19 @@ NORM_WEIGHT = "norm"     # random mode: 1 + N(0, 0.02), stored in float32
 
 @dataclass(frozen=True)
 class WeightSpec:
-    shape: tuple[int, ...]
+    shape: tuple[int, ...]           # an entry may be None: the stored tensor decides that size
     init: str = MATRIX
 
 
 @dataclass(frozen=True)
 class PagedKVSpec:
-    """Keys and values of every past token (or of the last ``window`` tokens) in pages."""
+    """Keys and values of every past token (or of the last ``window`` tokens, and of the
+    request's first ``keep_first`` tokens whatever the window) in pages."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: all keys are kept
+    v_head_dim: Optional[int] = None # None: values have the keys' head size
+    keep_first: int = 0              # a request's first tokens stay readable behind the window
 
 
 @dataclass(frozen=True)

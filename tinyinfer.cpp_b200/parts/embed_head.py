@@ -1,7 +1,8 @@
 """Token embedding and the output head.
 
 Embedding: ``x[t] = float32(E[token[t]])`` without scaling (reference:
-src/inference.cu:14-24).  Head: ``logits = h E_out^T`` in float32, where ``E_out``
+src/inference.cu:14-24); ``scaled_sinusoid``: the row times a constant plus a sine/cosine
+wave of the token's position.  Head: ``logits = h E_out^T`` in float32, where ``E_out``
 is the embedding table when the head is tied (reference: always tied,
 src/inference.cu:70-71) or a table of its own.
 """
@@ -32,6 +33,33 @@ class Embedding(Part):
         ops.embed(self.table, token_ids, out)
 
 
+class SinusoidEmbedding(Embedding):
+    """``x[t] = E[token[t]] * scale + s(p_t)``: the table's row times a constant, plus a fixed
+    wave of the token's position ``p``: ``s(p)[2i] = sin(p f_i)``, ``s(p)[2i+1] = cos(p f_i)``
+    with ``f_i = base ** (-2i / hidden_size)``.  ``f`` is made once on the host in double
+    precision and rounded to float32; angle, sine and cosine are float32 on the device.  A tied
+    head reads the table itself, without the constant."""
+    wants_positions = True
+
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, base: float = 10000.0,
+                 tensor: str = "weight"):
+        super().__init__(vocab_size, hidden_size)
+        self.scale, self.base, self.tensor = float(scale), float(base), str(tensor)
+        self.freq = None
+
+    def weight_specs(self):
+        return {self.tensor: WeightSpec((self.vocab_size, self.hidden_size), MATRIX)}
+
+    def load_weights(self, tensors, ops):
+        self.table = ops.pack_linear(tensors[self.tensor])
+        i = torch.arange((self.hidden_size + 1) // 2, dtype=torch.float64)
+        freq = torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * i / self.hidden_size)
+        self.freq = freq.to(torch.float32).to(self.table.device)
+
+    def forward(self, ops, token_ids, out, positions):
+        ops.embed_sinusoid(self.table, token_ids, positions, self.freq, self.scale, out)
+
+
 class LMHead(Part):
     category = "head"
 
@@ -58,4 +86,5 @@ class LMHead(Part):
 
 
 register_part("embedding", "embedding", Embedding)
+register_part("embedding", "scaled_sinusoid", SinusoidEmbedding)
 register_part("head", "lm_head", LMHead)

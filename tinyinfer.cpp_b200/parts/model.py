@@ -30,13 +30,14 @@ class CausalLM:
         for lp in plan.layers:
             parts = {
                 "mixer": build_part("mixer", lp.mixer),
-                "ffn": build_part("ffn", lp.ffn),
+                "ffn": None if lp.ffn is None else build_part("ffn", lp.ffn),
                 "mixer_norm": build_part("norm", lp.mixer_norm),
-                "ffn_norm": build_part("norm", lp.ffn_norm),
+                "ffn_norm": None if lp.ffn_norm is None else build_part("norm", lp.ffn_norm),
             }
             self.blocks.append(build_part("block", lp.block, **parts))
             for role, part in parts.items():
-                self._named.append((lp.names[role], part))
+                if part is not None:
+                    self._named.append((lp.names[role], part))
 
     # ---- weights -------------------------------------------------------------------------
     def expected_tensors(self) -> dict[str, WeightSpec]:
@@ -53,7 +54,8 @@ class CausalLM:
         published checkpoints with tied embeddings store the table twice).  The reference never
         reads a head of its own (src/model.cpp:120-121)."""
         if getattr(self.head, "tied", False):
-            return {self.plan.names["head"] + "weight": self.plan.names["embedding"] + "weight"}
+            local = getattr(self.embedding, "tensor", "weight")
+            return {self.plan.names["head"] + "weight": self.plan.names["embedding"] + local}
         return {}
 
     def load_weights(self, fetch: Callable[[str], torch.Tensor], ops) -> None:
@@ -91,7 +93,10 @@ class CausalLM:
         step.scratch.clear()           # what kernels derived from the step in an earlier pass is stale
         x = torch.empty((step.num_tokens, self.plan.hidden_size), dtype=torch.float32,
                         device=step.token_ids.device)
-        self.embedding.forward(ops, step.token_ids, x)
+        if getattr(self.embedding, "wants_positions", False):
+            self.embedding.forward(ops, step.token_ids, x, step.positions)
+        else:
+            self.embedding.forward(ops, step.token_ids, x)
         for entry in self.plan.schedule:
             cache = cache_views[(entry.cache_slot, entry.writes_cache)]
             self.blocks[entry.layer].forward(ops, x, step, cache)

@@ -1,0 +1,91 @@
+"""A routed feed-forward: per token the ``top`` of ``experts`` small gated feed-forwards, chosen
+by a sigmoid router, plus an optional shared expert behind a sigmoid gate of its own.
+
+* router logits ``z = Wr h`` in float32, scores ``s = sigmoid(z)``; the ``top`` largest are
+  chosen (ties: the lower index) and their scores are the weights, as they are.
+* a chosen expert ``e`` with weight ``w`` contributes ``Wdown_e (silu(Wgate_e x) * (Wup_e x))``
+  with ``x = w h``: the weight scales the expert's input.  The kernels use
+  ``Wgate_e (w h) = w (Wgate_e h)`` and apply ``w`` to both products in float32.
+* the shared expert (sizes of its own) runs on ``h`` for every token and its output is
+  multiplied by ``sigmoid(wsg . h)``, one number per token; ``wsg`` rides as one more row of the
+  router's product.
+* ``residual +=`` the sum.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .base import MATRIX, Part, WeightSpec, register_part
+
+
+class RoutedExperts(Part):
+    category = "ffn"
+
+    def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int,
+                 shared_size: Optional[int] = None):
+        if not 1 <= top <= experts:
+            raise ValueError(f"{top} of {experts} experts cannot be chosen")
+        self.hidden_size, self.experts, self.top = int(hidden_size), int(experts), int(top)
+        self.expert_size = int(expert_size)
+        self.shared_size = None if shared_size is None else int(shared_size)
+        self.w_router = self.w_gate = self.w_up = self.w_down = None
+        self.w_shared_gate_up = self.w_shared_down = None
+
+    def weight_specs(self):
+        h, f = self.hidden_size, self.expert_size
+        specs = {"router": WeightSpec((self.experts, h), MATRIX)}
+        for e in range(self.experts):
+            specs[f"e{e}.gate"] = WeightSpec((f, h), MATRIX)
+            specs[f"e{e}.up"] = WeightSpec((f, h), MATRIX)
+            specs[f"e{e}.down"] = WeightSpec((h, f), MATRIX)
+        if self.shared_size is not None:
+            s = self.shared_size
+            specs.update({"shared.gate": WeightSpec((s, h), MATRIX), "shared.up": WeightSpec((s, h), MATRIX),
+                          "shared.down": WeightSpec((h, s), MATRIX), "shared.sg": WeightSpec((1, h), MATRIX)})
+        return specs
+
+    def load_weights(self, tensors, ops):
+        def stacked(kind):
+            mats = [tensors[f"e{e}.{kind}"] for e in range(self.experts)]
+            if len({m.dtype for m in mats}) > 1:
+                mats = [m.to(torch.float32) for m in mats]
+            return torch.stack(mats, dim=0).contiguous()
+
+        router = [tensors["router"]]
+        if self.shared_size is not None:
+            router.append(tensors["shared.sg"])
+            g, u = tensors["shared.gate"], tensors["shared.up"]
+            if g.dtype != u.dtype:
+                g, u = g.to(torch.float32), u.to(torch.float32)
+            self.w_shared_gate_up = ops.pack_gate_up(g, u)
+            self.w_shared_down = ops.pack_linear(tensors["shared.down"])
+        if len({m.dtype for m in router}) > 1:
+            router = [m.to(torch.float32) for m in router]
+        rows = sum(m.shape[0] for m in router)
+        if rows % 16:                          # zero rows up to a width the tensor-core products take
+            router.append(torch.zeros((16 - rows % 16, self.hidden_size), dtype=router[0].dtype,
+                                      device=router[0].device))
+        self.w_router = ops.pack_linear(torch.cat(router, dim=0))
+        self.w_experts = ops.pack_experts(stacked("gate"), stacked("up"), stacked("down"))
+
+    def forward(self, ops, h, residual, step):
+        t = h.shape[0]
+        logits = torch.empty((t, self.w_router.shape[0]), dtype=torch.float32, device=h.device)
+        ops.linear(h, self.w_router, logits)
+        ids = torch.empty((t, self.top), dtype=torch.int32, device=h.device)
+        weights = torch.empty((t, self.top), dtype=torch.float32, device=h.device)
+        shared_gate = None
+        if self.shared_size is not None:
+            shared_gate = torch.empty((t,), dtype=torch.float32, device=h.device)
+        ops.router_topk(logits, self.experts, self.top, ids, weights, shared_gate)
+        ops.routed_experts(h, self.w_experts, ids, weights, residual)
+        if self.shared_size is not None:
+            y = torch.empty((t, self.shared_size), dtype=h.dtype, device=h.device)
+            ops.gate_up_swiglu(h, self.w_shared_gate_up, y)
+            ops.scale_rows(y, shared_gate)
+            ops.linear(y, self.w_shared_down, residual, accumulate=True)
+
+
+register_part("ffn", "routed_experts", RoutedExperts)

@@ -13,16 +13,17 @@ from .base import NORM_WEIGHT, Part, WeightSpec, as_float32, register_part
 class RMSNorm(Part):
     category = "norm"
 
-    def __init__(self, size: int, eps: float):
+    def __init__(self, size: int, eps: float, tensor: str = "weight"):
         self.size = int(size)
         self.eps = float(eps)
+        self.tensor = str(tensor)            # the weight's name behind the part's prefix (may be empty)
         self.weight: torch.Tensor | None = None
 
     def weight_specs(self):
-        return {"weight": WeightSpec((self.size,), NORM_WEIGHT)}
+        return {self.tensor: WeightSpec((self.size,), NORM_WEIGHT)}
 
     def load_weights(self, tensors, ops):
-        self.weight = as_float32(tensors["weight"]).contiguous()
+        self.weight = as_float32(tensors[self.tensor]).contiguous()
 
     def forward(self, ops, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         out = torch.empty((x.shape[0], self.size), dtype=out_dtype, device=x.device)

@@ -41,10 +41,13 @@ def check_tensors(where: str, expected: Mapping[str, WeightSpec],
     """``duplicates``: names that may be present although the model does not need them, each
     with the expected tensor it repeats; such a tensor is not "unexpected", but it must have the
     shape of the one it repeats."""
+    def fits(want, have) -> bool:              # None in a wanted shape: the tensor decides that size
+        return len(want) == len(have) and all(w is None or int(w) == int(h) for w, h in zip(want, have))
+
     missing = [n for n in expected if n not in found]
     unexpected = [n for n in found if n not in expected and n not in duplicates]
     wrong = [(n, expected[n].shape, found[n]) for n in expected
-             if n in found and tuple(found[n]) != tuple(expected[n].shape)]
+             if n in found and not fits(expected[n].shape, found[n])]
     wrong += [(n, expected[of].shape, found[n]) for n, of in duplicates.items()
               if n in found and n not in expected and of in expected
               and tuple(found[n]) != tuple(expected[of].shape)]

@@ -73,6 +73,9 @@ def random_tensor(seed: int, name: str, spec: WeightSpec, device="cpu",
         default = torch.bfloat16
     else:
         raise ValueError(f"tensor {name!r}: unknown initialisation class {spec.init!r}")
+    if any(d is None for d in spec.shape):
+        raise ValueError(f"tensor {name!r}: its shape {spec.shape} leaves a size to the stored tensor; "
+                         f"random weights need every size")
     key = _tensor_seed(seed, name)
     numel = 1
     for d in spec.shape:
