@@ -70,24 +70,32 @@ def attention_keys_values(h, w, prefix, mixer, eps):
     return unit_rms(k, eps), v
 
 
+def attend(q, keys, values, rel, heads_per_kv: int, scale: float, window: int, keep_first: int, far: int,
+           first_position: int = 0):
+    """Softmax attention of queries ``q`` [T, H, dk] at positions ``first_position ..`` over
+    ``keys`` [S, G, dk] and ``values`` [S, G, dv] at positions ``0 ..``; ``rel`` [rows, H]."""
+    t, nh, _ = q.shape
+    out = torch.zeros((t, nh, values.shape[2]), dtype=q.dtype)
+    for r in range(t):
+        i = first_position + r
+        js = [j for j in range(i + 1) if visible(i, j, window, keep_first)]
+        rows = [distance_bucket(i - j, rel.shape[0], far) for j in js]
+        for a in range(nh):
+            kv = a // heads_per_kv
+            s = keys[js, kv] @ q[r, a] * scale + rel[rows, a]
+            p = torch.softmax(s, dim=0)
+            out[r, a] = p @ values[js, kv]
+    return out
+
+
 def attention(h, w, prefix, mixer, eps, keys, values):
     """The mixer's output for all tokens of one sequence, given the keys and values to use."""
     t = h.shape[0]
     nh, g, dk, dv = mixer["heads"], mixer["kv_heads"], mixer["dim"], mixer["vdim"]
-    window, keep = mixer["mask"]["size"], mixer["mask"]["keep_first"]
-    rel = w[prefix + "rel"]
-    rows, far = rel.shape[0], mixer["bias_max"]
     q = unit_rms((h @ w[prefix + "q"].T + w[prefix + "q.b"]).view(t, nh, dk), eps)
+    heads = attend(q, keys, values, w[prefix + "rel"], nh // g, mixer["scale"], mixer["mask"]["size"],
+                   mixer["mask"]["keep_first"], mixer["bias_max"])
     gate = torch.sigmoid(h @ w[prefix + "g"].T)
-    heads = torch.zeros((t, nh, dv), dtype=h.dtype)
-    for i in range(t):
-        js = [j for j in range(i + 1) if visible(i, j, window, keep)]
-        for a in range(nh):
-            kv = a // (nh // g)
-            s = torch.stack([(q[i, a] * keys[j, kv]).sum() * mixer["scale"]
-                             + rel[distance_bucket(i - j, rows, far), a] for j in js])
-            p = torch.softmax(s, dim=0)
-            heads[i, a] = (p[:, None] * torch.stack([values[j, kv] for j in js])).sum(dim=0)
     return (heads.reshape(t, nh * dv) * gate) @ w[prefix + "o"].T
 
 
