@@ -112,7 +112,13 @@ def _attention_case(heads, kv, dk, dv, page_size, ctx_lens, q_lens, dtype, seed=
         req_of_tok += [i] * ql
     q = torch.randn((len(positions), heads, dk), generator=g)
     ti = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    step = SimpleNamespace(positions=ti(positions), req_of_tok=ti(req_of_tok), lists={}, scratch={},
+    # the lists the kernel set asks of a step (single-token rows, portions cut into its tiles)
+    from tinyinfer_b200.engine.batch import build_lists
+    from tinyinfer_b200.kernels import cuda_ops
+    lists = build_lists(cuda_ops(DEV).step_lists(torch.bfloat16), list(q_lens),
+                        [c - n for c, n in zip(ctx_lens, q_lens)])
+    step = SimpleNamespace(positions=ti(positions), req_of_tok=ti(req_of_tok), scratch={},
+                           lists={k: torch.from_numpy(a).to(torch.int32).to(DEV) for k, a in lists.items()},
                            max_position=max(ctx_lens), max_ctx_len=max(ctx_lens))
     pages = torch.zeros((num_pages, kv * page_size * (dk + dv)), dtype=dtype, device=DEV)
     cache = SimpleNamespace(pages=pages, block_table=bt.to(DEV), page_size=page_size, writes=True)
@@ -130,11 +136,12 @@ def _fill_pages(cache, bt, keys, values, kv, dk, dv):
             vpart[:, p % ps] = v[p].to(page.dtype)
 
 
-@pytest.mark.parametrize("geom", [(4, 2, 16, 24, 16), (6, 1, 32, 32, 8), (1, 1, 8, 8, 16), (8, 2, 64, 64, 64)])
+@pytest.mark.parametrize("geom", [(4, 2, 16, 24, 16), (6, 1, 32, 32, 8), (1, 1, 8, 8, 16), (8, 2, 64, 64, 64),
+                                  (4, 4, 128, 128, 32), (3, 1, 48, 48, 16)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_projection_bias_unit_norm_store_and_attention(ops, geom, dtype):
     heads, kv, dk, dv, ps = geom
-    ctx, ql = [90, 41, 7, 130], [90, 1, 3, 2]
+    ctx, ql = [90, 41, 7, 130, 300], [90, 1, 3, 2, 150]
     window, keep, far, rows = 20, 3, 40, 8
     step, cache, _, keys, values, bt = _attention_case(heads, kv, dk, dv, ps, ctx, ql, dtype, seed=2)
     _fill_pages(cache, bt, keys, values, kv, dk, dv)          # the context that earlier steps left
@@ -177,31 +184,32 @@ def test_projection_bias_unit_norm_store_and_attention(ops, geom, dtype):
         row += n
 
 
-@pytest.mark.parametrize("where", ["decoded", "portion"])
-def test_one_key_carries_the_weight_at_every_edge(ops, where):
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("where", ["decoded", "portion", "long portion"])
+def test_one_key_carries_the_weight_at_every_edge(ops, where, dtype):
     """One key stands out by a scaled query and key: its value comes back exactly when the mask
     lets it through, far back among hundreds, at a page's border, just inside and just outside
     the window, and among the kept first tokens."""
-    heads, kv, dk, dv, ps = 2, 1, 16, 8, 16
+    heads, kv, dk, dv, ps = 2, 1, 16, (8 if dtype == torch.float32 else 16), 16
     window, keep = 48, 5
     ctx = 400
-    n_new = 1 if where == "decoded" else 3
+    n_new = {"decoded": 1, "portion": 3, "long portion": 170}[where]
     last = ctx - 1
     cases = [(last - window + 1, True), (last - window, False), (keep - 1, True), (keep, False), (0, True),
              (last - 1, True), (last - 15, True), (last - 16, True), (352, True), (351, False), (200, False)]
     for target, seen in cases:
-        step, cache, q, keys, values, bt = _attention_case(heads, kv, dk, dv, ps, [ctx], [n_new], torch.float32, seed=4)
+        step, cache, q, keys, values, bt = _attention_case(heads, kv, dk, dv, ps, [ctx], [n_new], dtype, seed=4)
         keys[0].mul_(0.01)
         keys[0][target] = 3.0
         values[0][target] = torch.arange(1, dv + 1, dtype=torch.float32)
         _fill_pages(cache, bt, keys, values, kv, dk, dv)
         q.fill_(3.0)
-        qd = q.reshape(n_new, heads * dk).to(DEV)
-        out = torch.empty((n_new, heads * dv), dtype=torch.float32, device=DEV)
+        qd = q.reshape(n_new, heads * dk).to(DEV).to(dtype)
+        out = torch.empty((n_new, heads * dv), dtype=dtype, device=DEV)
         dist = torch.zeros((heads, 9), dtype=torch.float32, device=DEV)
         ops.biased_attention(qd, step, cache, out, heads, kv, dk, dv, window, keep, 1.0, dist, None)
-        got = out[-1].cpu().view(heads, dv)                       # the last row sits at position ctx - 1
-        hit = (got - torch.arange(1, dv + 1)).abs().max() < 1e-3
+        got = out[-1].float().cpu().view(heads, dv)               # the last row sits at position ctx - 1
+        hit = (got - torch.arange(1, dv + 1)).abs().max() < (1e-3 if dtype == torch.float32 else 0.1)
         assert bool(hit) == seen, f"key {target} seen from {last}: expected {'visible' if seen else 'hidden'}"
 
 
@@ -223,11 +231,11 @@ def test_distance_bias_reaches_the_scores(ops):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(7, 3, 40, 24, 24), (4, 4, 32, 16, None), (9, 1, 64, 32, 16)])
+@pytest.mark.parametrize("sizes", [(7, 3, 40, 24, 24, 37), (4, 4, 32, 16, None, 37), (9, 1, 64, 32, 16, 37),
+                                   (8, 2, 64, 96, 32, 301), (5, 5, 96, 32, None, 130), (16, 1, 128, 160, None, 700)])
 def test_router_and_experts(ops, dtype, sizes):
-    experts, top, width, ff, shared = sizes
+    experts, top, width, ff, shared, t = sizes
     g = torch.Generator().manual_seed(experts)
-    t = 37
     mlp = {"router": {"experts": experts, "top": top}, "expert": {"ff": ff}}
     w = {"router": (torch.randn((experts, width), generator=g) * 0.5).to(torch.bfloat16)}
     for e in range(experts):

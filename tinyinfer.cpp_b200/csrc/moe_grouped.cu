@@ -1,0 +1,265 @@
+// The experts' products of a routed feed-forward on the tensor cores (bfloat16, mma.sync), for
+// steps of many tokens.
+//
+//  1. moe_sort (one block): counts the (token, slot) pairs of every expert, lays the experts'
+//     pairs out one after the other (`sorted_slot[pos]` = token * top + slot) and lists the
+//     tiles of 64 rows, each inside one expert: {expert, first row, rows}.
+//  2. moe_grouped<GATED>: a block takes one tile of rows and 64 output columns of its expert:
+//     rows of h gathered by token, the expert's gate and up rows, float32 accumulation, and
+//     y = silu(w g) * (w u) in the epilogue (w: the pair's weight), stored in sorted order.
+//  3. moe_grouped<!GATED>: the same walk over y and the expert's down rows, 128 output columns a
+//     block; the float32 result goes to the pair's own row of a scratch.
+//  4. moe_combine: residual[t] += the rows of t's pairs, in slot order.
+//
+// No atomics touch a result, so a row's bits depend on its own operands only.  K is walked in
+// steps of 32 through a three-stage cp.async ring; warps are arranged 2 x 2 over a 64 x 128
+// tile of products (GATED: 64 gate and 64 up columns, interleaved in runs of 32 so that a warp
+// holds both values of its 32 outputs).
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 64, BNW = 128, BK = 32, STAGES = 3, THREADS = 128;
+constexpr int ROW_BYTES = BK * 2 + 16;                 // padded: ldmatrix rows fall in distinct banks
+constexpr int STAGE_BYTES = (BM + BNW) * ROW_BYTES;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+                 "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// meta: [0] = number of tiles.  tiles: [max_tiles][3] = {expert, first sorted row, rows}.
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ sorted_slot,
+                int* __restrict__ tiles, int* __restrict__ meta) {
+    extern __shared__ int sh[];                         // counts[experts], offsets[experts]
+    int* counts = sh;
+    int* offsets = sh + experts;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < experts) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, nt = 0;
+        for (int e = 0; e < experts; ++e) {
+            offsets[e] = at;
+            for (int r = 0; r < counts[e]; r += BM) {
+                tiles[nt * 3] = e;
+                tiles[nt * 3 + 1] = at + r;
+                tiles[nt * 3 + 2] = min(BM, counts[e] - r);
+                ++nt;
+            }
+            at += counts[e];
+            counts[e] = 0;                              // becomes the expert's cursor
+        }
+        meta[0] = nt;
+    }
+    __syncthreads();
+    // the order of an expert's pairs among themselves is left to the atomics: every row of a
+    // product is computed from its own operands alone, so no result depends on it
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < experts) sorted_slot[offsets[e] + atomicAdd(&counts[e], 1)] = i;
+    }
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(THREADS)
+moe_grouped_kernel(const bf16* a, int lda, const int* __restrict__ sorted_slot,
+                   const int* __restrict__ tiles, const int* __restrict__ meta, int top,
+                   const bf16* __restrict__ w0, const bf16* __restrict__ w1, int n, int k,
+                   const float* __restrict__ weights, bf16* __restrict__ y_sorted,
+                   float* __restrict__ out_rows) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ int row_src[BM];                         // the row of `a` behind each row of the tile
+    const int tile = blockIdx.y;
+    if (tile >= meta[0]) return;
+    const int expert = tiles[tile * 3], row0 = tiles[tile * 3 + 1], rows = tiles[tile * 3 + 2];
+    constexpr int BN_OUT = GATED ? BNW / 2 : BNW;       // output columns of a block
+    const int n0 = blockIdx.x * BN_OUT;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wm = warp >> 1, wn = warp & 1;
+    const int g = lane >> 2, tq = lane & 3;
+
+    if (threadIdx.x < BM) {
+        const int r = threadIdx.x;
+        int src = -1;
+        if (r < rows) src = GATED ? sorted_slot[row0 + r] / top : row0 + r;
+        row_src[r] = src;
+    }
+    __syncthreads();
+    const bf16* wg = w0 + (size_t)expert * n * k;
+    const bf16* wu = GATED ? w1 + (size_t)expert * n * k : nullptr;
+
+    // the weight row behind row r of the stage's B part
+    auto b_row = [&](int r) -> const bf16* {
+        if (GATED) {
+            const int half = r >> 6, in = r & 63;
+            const int col = n0 + half * 32 + (in & 31);
+            if (col >= n) return nullptr;
+            return (in < 32 ? wg : wu) + (size_t)col * k;
+        }
+        const int col = n0 + r;
+        return col < n ? wg + (size_t)col * k : nullptr;
+    };
+    auto issue = [&](int kb, int stage) {
+        unsigned char* as = smem + (size_t)stage * STAGE_BYTES;
+        unsigned char* bs = as + BM * ROW_BYTES;
+        const int k0 = kb * BK;
+        for (int c = threadIdx.x; c < BM * 4; c += THREADS) {
+            const int r = c >> 2, ch = c & 3;
+            const int src = row_src[r];
+            cp_async16(as + r * ROW_BYTES + ch * 16, src >= 0 ? a + (size_t)src * lda + k0 + ch * 8 : a, src >= 0);
+        }
+        for (int c = threadIdx.x; c < BNW * 4; c += THREADS) {
+            const int r = c >> 2, ch = c & 3;
+            const bf16* src = b_row(r);
+            cp_async16(bs + r * ROW_BYTES + ch * 16, src ? src + k0 + ch * 8 : w0, src != nullptr);
+        }
+    };
+
+    float acc[2][8][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.0f;
+
+    const int kbs = k / BK;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < kbs) issue(s, s);
+        cp_async_commit();
+    }
+    for (int kb = 0; kb < kbs; ++kb) {
+        if (kb + STAGES - 1 < kbs) issue(kb + STAGES - 1, (kb + STAGES - 1) % STAGES);
+        cp_async_commit();
+        cp_async_wait<STAGES - 1>();
+        __syncthreads();
+        const unsigned char* as = smem + (size_t)(kb % STAGES) * STAGE_BYTES;
+        const unsigned char* bs = as + BM * ROW_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BK / 16; ++kk) {
+            unsigned af[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                ldmatrix_x4(af[i], as + (wm * 32 + i * 16 + (lane & 15)) * ROW_BYTES + (kk * 16 + (lane >> 4) * 8) * 2);
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {
+                unsigned b[4];
+                const int col = wn * 64 + jp * 16 + (lane >> 4) * 8 + (lane & 7);
+                const int kd = kk * 16 + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4(b, bs + col * ROW_BYTES + kd * 2);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    mma_bf16(acc[i][2 * jp], af[i], b[0], b[1]);
+                    mma_bf16(acc[i][2 * jp + 1], af[i], b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = wm * 32 + i * 16 + g + 8 * half;
+            if (r >= rows) continue;
+            if (GATED) {
+                const float w = weights[sorted_slot[row0 + r]];
+                bf16* dst = y_sorted + (size_t)(row0 + r) * n;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int col = n0 + wn * 32 + j * 8 + tq * 2;
+                    if (col >= n) continue;
+                    const float g0 = acc[i][j][2 * half] * w, g1 = acc[i][j][2 * half + 1] * w;
+                    const float u0 = acc[i][j + 4][2 * half] * w, u1 = acc[i][j + 4][2 * half + 1] * w;
+                    const float y0 = g0 / (1.0f + __expf(-g0)) * u0, y1 = g1 / (1.0f + __expf(-g1)) * u1;
+                    *reinterpret_cast<__nv_bfloat162*>(dst + col) = __floats2bfloat162_rn(y0, y1);
+                }
+            } else {
+                float* dst = out_rows + (size_t)sorted_slot[row0 + r] * n;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int col = n0 + wn * 64 + j * 8 + tq * 2;
+                    if (col >= n) continue;
+                    *reinterpret_cast<float2*>(dst + col) = make_float2(acc[i][j][2 * half], acc[i][j][2 * half + 1]);
+                }
+            }
+        }
+    }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ rows, int top, int width, int num_tokens,
+                                   float* __restrict__ residual, int res_stride) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)num_tokens * width) return;
+    const int t = (int)(i / width), c = (int)(i % width);
+    float total = 0.0f;
+    for (int s = 0; s < top; ++s) total += rows[((size_t)t * top + s) * width + c];
+    residual[(size_t)t * res_stride + c] += total;
+}
+
+}  // namespace
+
+extern "C" int ti_moe_grouped_supported(int width, int ff, int experts) {
+    return width % 32 == 0 && ff % 32 == 0 && experts >= 1 && experts <= 4096;
+}
+
+// Scratch the caller brings: sorted_slot int32 [pairs], tiles int32 [(pairs / 64 + experts) * 3],
+// meta int32 [1], y_sorted bfloat16 [pairs, ff], out_rows float32 [pairs, width].
+extern "C" int ti_moe_grouped(const void* h, int h_stride, const void* w_gate, const void* w_up,
+                              const void* w_down, const int* ids, const float* weights, int num_tokens,
+                              int top, int experts, int width, int ff, int* sorted_slot, int* tiles,
+                              int* meta, void* y_sorted, float* out_rows, float* residual,
+                              int res_stride, void* stream) {
+    if (num_tokens == 0) return 0;
+    TI_REQUIRE(ti_moe_grouped_supported(width, ff, experts),
+               "moe_grouped: width %d and expert size %d must be multiples of 32", width, ff);
+    TI_REQUIRE(h_stride % 8 == 0 && ((uintptr_t)h) % 16 == 0, "moe_grouped: rows of h must be 16-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int pairs = num_tokens * top;
+    const int max_tiles = pairs / BM + experts;
+    TI_REQUIRE(max_tiles <= 65535, "moe_grouped: %d tiles exceed the grid limit", max_tiles);
+    moe_sort_kernel<<<1, 1024, 2 * experts * sizeof(int), s>>>(ids, pairs, experts, sorted_slot, tiles, meta);
+    constexpr int SMEM = STAGES * STAGE_BYTES;
+    static TiPerDevice configured;
+    if (configured.first_use()) {
+        cudaError_t e1 = cudaFuncSetAttribute(moe_grouped_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e2 = cudaFuncSetAttribute(moe_grouped_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e1 != cudaSuccess || e2 != cudaSuccess) return ti_fail("moe_grouped: cannot set the shared memory size");
+        configured.mark();
+    }
+    dim3 g1((ff + BNW / 2 - 1) / (BNW / 2), max_tiles);
+    moe_grouped_kernel<true><<<g1, THREADS, SMEM, s>>>(
+        (const bf16*)h, h_stride, sorted_slot, tiles, meta, top, (const bf16*)w_gate, (const bf16*)w_up, ff, width,
+        weights, (bf16*)y_sorted, nullptr);
+    dim3 g2((width + BNW - 1) / BNW, max_tiles);
+    moe_grouped_kernel<false><<<g2, THREADS, SMEM, s>>>(
+        (const bf16*)y_sorted, ff, sorted_slot, tiles, meta, top, (const bf16*)w_down, nullptr, width, ff,
+        nullptr, nullptr, out_rows);
+    const size_t total = (size_t)num_tokens * width;
+    moe_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(out_rows, top, width, num_tokens,
+                                                                       residual, res_stride);
+    return ti_check_launch("moe_grouped");
+}

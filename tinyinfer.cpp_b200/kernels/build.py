@@ -27,6 +27,8 @@ LIBRARIES = {
     "bf16": ["common.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2sm.cu",
              "gemm_tcgen05_few.cu", "ffn_decode.cu", "attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu",
              "attn_prefill_tc2.cu"],
+    # tensor-core kernels of the attention with a distance bias and of the routed feed-forward
+    "bf16_gated": ["common.cu", "attn_gated_bias_tc.cu", "moe_grouped.cu"],
 }
 
 # libraries that parts bring themselves: name -> (absolute source paths, include folders)

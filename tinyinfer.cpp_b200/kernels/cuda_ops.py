@@ -127,6 +127,9 @@ class CudaOps:
         self._declare()
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._bf16 = None
+        self._gated = None
+        self.use_tc_biased_attention = True   # tensor-core prompt kernel of the attention with a distance bias
+        self.grouped_experts_from = 128       # (token, slot) pairs from which the experts run as grouped products
         self._counters = None
         self.use_tc_attention = True      # tcgen05 prompt attention where the shape allows
         self.use_2sm_gemm = True          # pairs of SMs for products with enough 256 x 256 tiles
@@ -254,6 +257,22 @@ class CudaOps:
             self._tile_rows = (int(b.ti_attn_prefill_tile_rows()), int(b.ti_attn_prefill_tc_tile_rows()))
             self._bf16 = b
         return self._bf16
+
+    @property
+    def gated(self):
+        """The tensor-core kernels of the attention with a distance bias and of the routed
+        feed-forward (bfloat16), built and loaded when first needed."""
+        if self._gated is None:
+            b = load_library("bf16_gated")
+            b.ti_last_error.restype = ctypes.c_char_p
+            b.ti_attn_bias_prefill_supported.argtypes = [_i, _i, _i]
+            b.ti_attn_bias_prefill.argtypes = [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f,
+                                               _vp, _i, _vp, _i, _vp, _vp, _vp]
+            b.ti_moe_grouped_supported.argtypes = [_i, _i, _i]
+            b.ti_moe_grouped.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp,
+                                         _vp, _vp, _i, _vp]
+            self._gated = b
+        return self._gated
 
     def step_lists(self, act_dtype):
         """The host-built integer lists (``engine.batch.StepList``) that the attention kernels of
@@ -861,10 +880,29 @@ class CudaOps:
         _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1
                                and tuple(gate.shape) == (t, num_heads * dv)),
               "biased_attention: the gate must be float32 [tokens, heads * dv]")
+        rows, n_rows = None, t
+        lists = step.lists
+        if (self.use_tc_biased_attention and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16
+                and dist_bias is not None and "single_rows" in lists
+                and (gate is None or (gate.stride(0) % 2 == 0 and gate.data_ptr() % 8 == 0))
+                and self.gated.ti_attn_bias_prefill_supported(dk, dv, cache.page_size)):
+            self.bf16
+            tiles = lists[f"portion_tiles_{self._tile_rows[0]}"]
+            if tiles.shape[0]:
+                self._ok(self.gated.ti_attn_bias_prefill(
+                    q.data_ptr(), tiles.data_ptr(), tiles.shape[0], step.positions.data_ptr(), bt.data_ptr(),
+                    bt.stride(0), pages.data_ptr(), pages.shape[0], cache.page_size, num_heads, num_kv_heads, dk,
+                    int(window or 0), int(keep_first), float(scale), dist_bias.data_ptr(), dist_bias.shape[1],
+                    _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(),
+                    self.status.data_ptr(), self._stream()), self.gated)
+                rows = lists["single_rows"]
+                n_rows = rows.shape[0]
+                if n_rows == 0:
+                    return
         self._ok(self.core.ti_attention_bias_simple(
-            q.data_ptr(), _code(q, "q"), None, step.positions.data_ptr(), step.req_of_tok.data_ptr(),
+            q.data_ptr(), _code(q, "q"), _ptr(rows), step.positions.data_ptr(), step.req_of_tok.data_ptr(),
             bt.data_ptr(), bt.stride(0), pages.data_ptr(), _code(pages, "cache"), pages.shape[0],
-            cache.page_size, t, num_heads, num_kv_heads, dk, dv, int(window or 0), int(keep_first),
+            cache.page_size, n_rows, num_heads, num_kv_heads, dk, dv, int(window or 0), int(keep_first),
             float(scale), _ptr(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0,
             _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(),
             self.status.data_ptr(), self._stream()))
@@ -902,6 +940,21 @@ class CudaOps:
         _need(residual.dtype == torch.float32 and residual.stride(1) == 1 and tuple(residual.shape) == (t, width),
               "routed_experts: float32 residual")
         _need(h.stride(1) == 1, "routed_experts: rows must be contiguous")
+        if (self.grouped_experts_from is not None and t * top >= self.grouped_experts_from
+                and h.dtype == torch.bfloat16 and w["gate"].dtype == torch.bfloat16
+                and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
+                and self.gated.ti_moe_grouped_supported(width, ff, experts)):
+            pairs = t * top
+            ints = torch.empty(pairs + 3 * (pairs // 64 + experts) + 1, dtype=torch.int32, device=h.device)
+            y_sorted = torch.empty((pairs, ff), dtype=torch.bfloat16, device=h.device)
+            out_rows = torch.empty((pairs, width), dtype=torch.float32, device=h.device)
+            self._ok(self.gated.ti_moe_grouped(
+                h.data_ptr(), h.stride(0), w["gate"].data_ptr(), w["up"].data_ptr(), w["down"].data_ptr(),
+                ids.data_ptr(), weights.data_ptr(), t, top, experts, width, ff, ints.data_ptr(),
+                ints[pairs:].data_ptr(), ints[ints.shape[0] - 1:].data_ptr(), y_sorted.data_ptr(),
+                out_rows.data_ptr(), residual.data_ptr(), residual.stride(0), self._stream()), self.gated)
+            self.launches += 3
+            return
         y = torch.empty((t, top, ff), dtype=h.dtype, device=h.device)
         self._ok(self.core.ti_moe_gate_up_simple(
             h.data_ptr(), _code(h, "routed_experts"), h.stride(0), w["gate"].data_ptr(), w["up"].data_ptr(),
