@@ -26,6 +26,17 @@ points     decode tokens a second at batch 1 and 64, the same steps without a CU
 points_frac  for each point its fraction of its roofline (decode: bytes / time / copy bandwidth;
            prefill: flops / time / the bf16 peak, the sustained one for steps over 5 ms).
 
+``--design kagorax`` leaves all of the above alone and instead prints one JSON line that sets
+the Kagorax decoder (attention with a distance bias, kept first tokens and an output gate; a
+routed feed-forward) beside the Qwen3 decoder at equal sizes: the same width, heads and window
+in every layer, and a dense feed-forward as wide as the rows a token uses of the routed one
+(top x expert size + the shared expert).  Per size: the prefill of one prompt and graph-replayed
+decode steps of both, in tokens a second, and, from one eager step of each with CUDA events
+around the kernel set's calls while the device is kept busy, the time per layer of the kernels
+that differ (prompt attention, single-token attention, feed-forward) with each one's fraction of
+its roofline: flops / time / bf16 peak for prompt kernels, bytes / time / copy bandwidth for
+the kernels of a decode step.
+
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from an earlier
 measurement on this pool (6.65 TB/s, 1.59 PFLOP/s), and the fractions say which.  The working
 set (1.2 GB of weights and gigabytes of cache) is far larger than the 126 MB L2, so no flush is
@@ -410,6 +421,136 @@ def shape_points(shape_key, page_size, context, steps, warmup, batches, prefill,
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 
 
+# ---- the Kagorax decoder beside the Qwen3 decoder at equal sizes --------------------------------
+# (width, heads, kv heads, head size, window, kept first tokens, experts, top, expert size, shared size, layers)
+DESIGN_SIZES = {
+    "w1024": (1024, 16, 8, 128, 1024, 4, 32, 4, 512, 1024, 8),
+    "w2048": (2048, 32, 4, 128, 2048, 4, 64, 8, 768, 768, 6),
+    "w4096_h64": (4096, 64, 8, 64, 4096, 16, 32, 2, 2048, 2048, 4),
+}
+DESIGN_VOCAB = 32768
+
+
+def kagorax_config(size):
+    w, h, g, d, win, keep, experts, top, ff, shared, layers = size
+    layer = {"type": "attention",
+             "mixer": {"heads": h, "kv_heads": g, "dim": d, "vdim": d, "scale": d ** -0.5, "bias_max": 4 * win,
+                       "bias_rows": 32, "mask": {"size": win, "keep_first": keep}},
+             "mlp": {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff},
+                     "shared": {"ff": shared}}}
+    return {"architecture": "Kagorax", "vocab": DESIGN_VOCAB, "width": w, "embedding": {"scale": float(w) ** 0.5},
+            "norm": {"eps": 1e-5}, "layers": [layer] * layers}
+
+
+def qwen3_like_config(size, context):
+    w, h, g, d, win, keep, experts, top, ff, shared, layers = size
+    return dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=layers, hidden_size=w,
+                num_attention_heads=h, num_key_value_heads=g, head_dim=d, intermediate_size=top * ff + shared,
+                vocab_size=DESIGN_VOCAB, rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=True,
+                max_position_embeddings=context, sliding_window=win, layer_types=["sliding_attention"] * layers)
+
+
+def timed_ops(engine, names, run, torch):
+    """Milliseconds the device spends inside each named call of the kernel set during ``run()``:
+    CUDA events around every call, with the device kept busy beforehand so that the host's
+    launches run ahead of it."""
+    ops = engine.ops
+    spans = {n: [] for n in names}
+    originals = {n: getattr(ops, n) for n in names}
+
+    def wrap(name, fn):
+        def inner(*a, **k):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            out = fn(*a, **k)
+            a1.record()
+            spans[name].append((a0, a1))
+            return out
+        return inner
+
+    for n in names:
+        setattr(ops, n, wrap(n, originals[n]))
+    try:
+        torch.cuda.synchronize()
+        torch.cuda._sleep(3_000_000)                 # about 2 ms: the launches queue up behind it
+        run()
+        torch.cuda.synchronize()
+    finally:
+        for n in names:
+            delattr(ops, n)
+    return {n: [a.elapsed_time(b) for a, b in v] for n, v in spans.items()}
+
+
+def design_arm(args) -> int:
+    import torch
+    from tinyinfer_b200 import Engine, StepEntry
+    pk, pk_kind = peaks()
+    prompt_len, batch, context = args.prefill_tokens, args.batch, args.context
+    warmup = max(args.warmup, 3)
+    out = {"design": "kagorax", "beside": "qwen3 at equal sizes", "peaks": pk_kind, "prefill_tokens": prompt_len,
+           "decode_batch": batch, "decode_context": context, "dtype": "bf16", "data": "synthetic", "sizes": {}}
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, DESIGN_VOCAB, (prompt_len,), generator=g).tolist()
+    for key, size in DESIGN_SIZES.items():
+        if args.design_size and key != args.design_size:
+            continue
+        w, h, kvh, d, win, keep, experts, top, ff, shared, layers = size
+        res = {}
+        # rooflines of the kernels that differ, per layer
+        seen = sum(min(i + 1, win) + min(keep, max(0, i + 1 - win)) for i in range(prompt_len))
+        attn_flops = 4.0 * h * d * seen
+        dec_keys = min(context, win + keep)
+        attn_bytes = batch * kvh * dec_keys * 2 * d * 2.0
+        ffn_flops = {"kagorax": 2.0 * prompt_len * 3 * w * (top * ff + shared), "qwen3": 2.0 * prompt_len * 3 * w * (top * ff + shared)}
+        ffn_bytes = {"kagorax": 2.0 * 3 * w * (min(experts, batch * top) * ff + shared), "qwen3": 2.0 * 3 * w * (top * ff + shared)}
+        for arm, cfg, calls in (
+                ("kagorax", kagorax_config(size), {"attention": ["biased_attention"], "ffn": ["router_topk", "routed_experts", "gate_up_swiglu", "scale_rows"]}),
+                ("qwen3", qwen3_like_config(size, max(context, prompt_len) + 64), {"attention": ["paged_attention"], "ffn": ["swiglu_ffn"]})):
+            engine = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=args.page_size,
+                            num_pages=-(-max(batch * context, prompt_len) // args.page_size) + batch + 2,
+                            max_requests=batch + 1, step_graphs=True)
+            pf_ms = measure_prefill(engine, prompt_len, max(1, min(args.steps, 6)), torch)
+            ms, clocks, launches = measure_decode(engine, batch, context, args.steps, warmup, torch)
+            a = {"prefill_tok_s": round(prompt_len / pf_ms * 1e3), "prefill_ms": round(pf_ms, 3),
+                 "decode_tok_s": round(batch / ms * 1e3, 1), "decode_ms_per_step": round(ms, 4),
+                 "decode_launches_per_step": launches // max(1, args.steps), "clocks": clocks}
+            names = calls["attention"] + calls["ffn"] + (["linear"] if arm == "kagorax" else [])
+            engine._step_graphs = None
+            engine.ops.fuse_decode_tail = engine.ops.fuse_decode_ffn = False   # the feed-forward as a call of its own
+            spans = timed_ops(engine, names, lambda: engine.step([StepEntry("p", prompt, [prompt_len - 1])]), torch)
+            engine.finish("p")
+            ids = fill_requests(engine, batch, context - 4, torch)
+            dspans = timed_ops(engine, names, lambda: engine.step([StepEntry(r, [1], [0]) for r in ids]), torch)
+            for r in ids:
+                engine.finish(r)
+
+            def per_layer(sp, which):
+                return sum(sum(sp[n]) for n in calls[which]) / layers
+
+            if arm == "kagorax":          # a layer calls `linear` four times: projections, output, router,
+                lin, dlin = spans["linear"], dspans["linear"]      # and the shared expert's down product
+                extra = sum(lin[i] for i in range(min(len(lin), 4 * layers)) if i % 4 >= 2) / layers
+                dextra = sum(dlin[i] for i in range(min(len(dlin), 4 * layers)) if i % 4 >= 2) / layers
+            else:
+                extra = dextra = 0.0
+            pa, da = per_layer(spans, "attention"), per_layer(dspans, "attention")
+            pff, dff = per_layer(spans, "ffn") + extra, per_layer(dspans, "ffn") + dextra
+            a["per_layer_us"] = {"prompt_attention": round(pa * 1e3, 1), "decode_attention": round(da * 1e3, 1),
+                                 "prompt_ffn": round(pff * 1e3, 1), "decode_ffn": round(dff * 1e3, 1)}
+            a["roofline_frac"] = {
+                "prompt_attention": round(attn_flops / (pa * 1e-3) / (pk["bf16_tflops"] * 1e12), 3),
+                "decode_attention": round(attn_bytes / (da * 1e-3) / (pk["hbm_gbs"] * 1e9), 3),
+                "prompt_ffn": round(ffn_flops[arm] / (pff * 1e-3) / (pk["bf16_tflops"] * 1e12), 3),
+                "decode_ffn": round(ffn_bytes[arm] / (dff * 1e-3) / (pk["hbm_gbs"] * 1e9), 3)}
+            res[arm] = a
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][key] = {"width": w, "heads": h, "kv_heads": kvh, "head_dim": d, "window": win, "keep_first": keep,
+                             "experts": experts, "top": top, "expert_ff": ff, "shared_ff": shared, "layers": layers, **res}
+    print(json.dumps(out))
+    return 0
+
+
 def reference_binary():
     """The reference's command-line program, built with its own CMakeLists if it is not there yet.
     Returns (path, None) or (None, why not)."""
@@ -561,6 +702,9 @@ def main() -> int:
                     help="with --only mixed: the number of decoding requests beside the 512-token portion")
     ap.add_argument("--attention-in-turn", action="store_true",
                     help="with --only mixed: flash-decoding behind the prompt attention kernel, not beside it")
+    ap.add_argument("--design", choices=["kagorax"], default=None,
+                    help="set this decoder beside the Qwen3 decoder at equal sizes instead of the default run")
+    ap.add_argument("--design-size", choices=list(DESIGN_SIZES), default=None, help="one of the sizes only")
     ap.add_argument("--only", choices=["decode", "prefill", "chains", "mixed"], default=None,
                     help="run one part only and print a short line (for profiling small cases)")
     args = ap.parse_args()
@@ -571,6 +715,8 @@ def main() -> int:
         print(f"bench.py measures one GPU; this engine does no work on several (asked for {args.gpus})")
         return 2
     warmup = max(args.warmup, 3)
+    if args.design:
+        return design_arm(args)
 
     import torch
     from tinyinfer_b200 import LLM

@@ -275,6 +275,233 @@ attn_bias_prefill_kernel(const bf16* __restrict__ q, const int* __restrict__ til
     }
 }
 
+// Single-token rows.  A block takes one row and one kv head: the group's query heads are the rows
+// of the MMA, and the block's four warps take the tiles of 32 keys in turn (tile i of the walk
+// goes to warp i mod 4), each through a two-stage cp.async ring of its own; at the end the warps'
+// partial results meet in shared memory, are added in warp order and gated.  The walk and the
+// mask are those of the prompt kernel; the bias comes straight from the table.
+constexpr int DT = 32;
+constexpr int DWARPS = 4;
+
+template <int HD>
+__global__ void __launch_bounds__(DWARPS * 32)
+attn_bias_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows,
+                        const int* __restrict__ positions, const int* __restrict__ req_of_tok,
+                        const int* __restrict__ block_table, int bt_stride,
+                        const bf16* __restrict__ pages, int num_pages, int page_size, int num_heads,
+                        int num_kv_heads, int window, int keep_first, float scale,
+                        const float* __restrict__ dist_bias, int n_dist, const float* gate,
+                        int gate_stride, bf16* __restrict__ out, int* __restrict__ status) {
+    constexpr int ROW_BYTES = HD * 2 + 16;
+    constexpr int CHUNKS = HD / 8;
+    constexpr int KSTEPS = HD / 16;
+    constexpr int NT_O = HD / 8;
+    constexpr int WARP_SMEM = 2 * 2 * DT * ROW_BYTES;
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ float sm_m[DWARPS][16], sm_l[DWARPS][16];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, tq = lane & 3;
+    const int t = rows[blockIdx.x], kvh = blockIdx.y;
+    const int group = num_heads / num_kv_heads;
+    const int pos = positions[t], ctx = pos + 1;
+    const int* table = block_table + (size_t)req_of_tok[t] * bt_stride;
+    const size_t kv_stride = (size_t)num_kv_heads * page_size * HD;
+    const int lo = window > 0 ? max(0, ctx - window) : 0;
+    const int tile_lo = lo / DT, tile_hi = (ctx + DT - 1) / DT;
+    const int n_pre = min(tile_lo, (keep_first + DT - 1) / DT);
+    const int n_walk = n_pre + (tile_hi - tile_lo);
+    auto tile_of = [&](int i) { return i < n_pre ? i : tile_lo + (i - n_pre); };
+    unsigned char* mine = smem + (size_t)warp * WARP_SMEM;
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    float o[NT_O][4];
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+
+    auto issue = [&](int tile, int stage) {
+        unsigned char* kdst = mine + (size_t)stage * 2 * DT * ROW_BYTES;
+        unsigned char* vdst = kdst + DT * ROW_BYTES;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int key0 = tile * DT + r * 16;
+            int pg = -1;
+            if (key0 < ctx && (key0 + 16 > lo || key0 < keep_first)) {
+                pg = table[key0 / page_size];
+                if (pg < 0 || pg >= num_pages) {
+                    if (lane == 0) atomicCAS(status, 0, 1);
+                    pg = -1;
+                }
+            }
+            const bool valid = pg >= 0;
+            const bf16* ksrc = pages;
+            if (valid)
+                ksrc = pages + (((size_t)pg * 2 * num_kv_heads + kvh) * page_size + key0 % page_size) * HD;
+            const bf16* vsrc = valid ? ksrc + kv_stride : pages;
+            for (int c = lane; c < 16 * CHUNKS; c += 32) {
+                const int off = (r * 16 + c / CHUNKS) * ROW_BYTES + (c % CHUNKS) * 16;
+                cp_async16(kdst + off, ksrc + (valid ? c * 8 : 0), valid);
+                cp_async16(vdst + off, vsrc + (valid ? c * 8 : 0), valid);
+            }
+        }
+    };
+
+    if (warp < n_walk) {
+        unsigned qa[KSTEPS][4];
+        const bf16* qbase = q + ((size_t)t * num_heads + (size_t)kvh * group) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const int k0 = ks * 16 + tq * 2;
+            qa[ks][0] = g < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)g * HD + k0) : 0u;
+            qa[ks][1] = g + 8 < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)(g + 8) * HD + k0) : 0u;
+            qa[ks][2] = g < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)g * HD + k0 + 8) : 0u;
+            qa[ks][3] = g + 8 < group ? *reinterpret_cast<const unsigned*>(qbase + (size_t)(g + 8) * HD + k0 + 8) : 0u;
+        }
+        const float* bias_r[2] = {dist_bias + (size_t)(kvh * group + min(g, group - 1)) * n_dist,
+                                  dist_bias + (size_t)(kvh * group + min(g + 8, group - 1)) * n_dist};
+        issue(tile_of(warp), 0);
+        cp_async_commit();
+        int turn = 0;
+        for (int wi = warp; wi < n_walk; wi += DWARPS, ++turn) {
+            const int tile = tile_of(wi);
+            const int stage = turn & 1;
+            if (wi + DWARPS < n_walk) issue(tile_of(wi + DWARPS), stage ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+            __syncwarp();
+            const unsigned char* ks = mine + (size_t)stage * 2 * DT * ROW_BYTES;
+            const unsigned char* vs = ks + DT * ROW_BYTES;
+            float s_acc[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s_acc[j][0] = s_acc[j][1] = s_acc[j][2] = s_acc[j][3] = 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+                for (int jp = 0; jp < 2; ++jp) {
+                    unsigned b[4];
+                    const int key = jp * 16 + (lane >> 4) * 8 + (lane & 7);
+                    const int dim = kk * 16 + ((lane >> 3) & 1) * 8;
+                    ldmatrix_x4(b, ks + key * ROW_BYTES + dim * 2);
+                    mma_bf16(s_acc[2 * jp], qa[kk], b[0], b[1]);
+                    mma_bf16(s_acc[2 * jp + 1], qa[kk], b[2], b[3]);
+                }
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = tile * DT + j * 8 + tq * 2 + (e & 1);
+                    float v = -INFINITY;
+                    if (key < ctx && (key >= lo || key < keep_first))
+                        v = (s_acc[j][e] * scale + __ldg(bias_r[e >> 1] + min(pos - key, n_dist - 1))) * LOG2E;
+                    s_acc[j][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            }
+            float alpha[2], m_use[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r]);
+                alpha[r] = m_new == -INFINITY ? 1.0f : exp2f(m_run[r] - m_new);
+                m_run[r] = m_new;
+                m_use[r] = m_new == -INFINITY ? 0.0f : m_new;
+            }
+            float sum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p = exp2f(s_acc[j][e] - m_use[e >> 1]);
+                    s_acc[j][e] = p;
+                    sum[e >> 1] += p;
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + sum[r];
+#pragma unroll
+            for (int i = 0; i < NT_O; ++i) {
+                o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+                o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+            }
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+                unsigned pa[4];
+                pa[0] = pack_bf16(s_acc[2 * kk][0], s_acc[2 * kk][1]);
+                pa[1] = pack_bf16(s_acc[2 * kk][2], s_acc[2 * kk][3]);
+                pa[2] = pack_bf16(s_acc[2 * kk + 1][0], s_acc[2 * kk + 1][1]);
+                pa[3] = pack_bf16(s_acc[2 * kk + 1][2], s_acc[2 * kk + 1][3]);
+#pragma unroll
+                for (int dp = 0; dp < NT_O / 2; ++dp) {
+                    unsigned b[4];
+                    const int key = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                    const int dim = dp * 16 + (lane >> 4) * 8;
+                    ldmatrix_x4_trans(b, vs + key * ROW_BYTES + dim * 2);
+                    mma_bf16(o[2 * dp], pa, b[0], b[1]);
+                    mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
+                }
+            }
+            __syncwarp();
+        }
+        cp_async_wait<0>();
+        __syncwarp();
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    // the warp's partial result takes the place of its tiles: [16 heads][HD] float32
+    float* po = reinterpret_cast<float*>(mine);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+#pragma unroll
+        for (int i = 0; i < NT_O; ++i)
+            *reinterpret_cast<float2*>(po + (g + 8 * r) * HD + i * 8 + tq * 2) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+        if (tq == 0) { sm_m[warp][g + 8 * r] = m_run[r]; sm_l[warp][g + 8 * r] = l_run[r]; }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < group * HD; idx += DWARPS * 32) {
+        const int r = idx / HD, d = idx % HD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DWARPS; ++w) mm = fmaxf(mm, sm_m[w][r]);
+        float total = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < DWARPS; ++w) {
+            const float wt = sm_m[w][r] == -INFINITY ? 0.0f : exp2f(sm_m[w][r] - mm);
+            total += sm_l[w][r] * wt;
+            acc += reinterpret_cast<const float*>(smem + (size_t)w * WARP_SMEM)[r * HD + d] * wt;
+        }
+        float y = acc / total;
+        const int head = kvh * group + r;
+        if (gate) y *= 1.0f / (1.0f + __expf(-gate[(size_t)t * gate_stride + (size_t)head * HD + d]));
+        out[((size_t)t * num_heads + head) * HD + d] = __float2bfloat16_rn(y);
+    }
+}
+
+template <int HD>
+int launch_decode(const bf16* q, const int* rows, int num_rows, const int* positions, const int* req_of_tok,
+                  const int* block_table, int bt_stride, const bf16* pages, int num_pages, int page_size,
+                  int num_heads, int num_kv_heads, int window, int keep_first, float scale,
+                  const float* dist_bias, int n_dist, const float* gate, int gate_stride, bf16* out,
+                  int* status, cudaStream_t s) {
+    constexpr int SMEM = DWARPS * 2 * 2 * DT * (HD * 2 + 16);
+    static TiPerDevice configured;
+    if (configured.first_use()) {
+        cudaError_t e = cudaFuncSetAttribute(attn_bias_decode_kernel<HD>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return ti_fail("attn_bias_decode: %s", cudaGetErrorString(e));
+        configured.mark();
+    }
+    dim3 grid(num_rows, num_kv_heads);
+    attn_bias_decode_kernel<HD><<<grid, DWARPS * 32, SMEM, s>>>(
+        q, rows, positions, req_of_tok, block_table, bt_stride, pages, num_pages, page_size, num_heads,
+        num_kv_heads, window, keep_first, scale, dist_bias, n_dist, gate, gate_stride, out, status);
+    return ti_check_launch("attn_bias_decode");
+}
+
 template <int HD>
 int launch_prefill(const bf16* q, const int* tiles, int num_tiles, const int* positions,
                    const int* block_table, int bt_stride, const bf16* pages, int num_pages,
@@ -334,4 +561,36 @@ extern "C" int ti_attn_bias_prefill(const void* q, const int* tiles, int num_til
     }
 #undef CASE
     return ti_fail("attn_bias_prefill: head_dim %d", head_dim);
+}
+
+extern "C" int ti_attn_bias_decode_supported(int dk, int dv, int group, int page_size) {
+    return dk == dv && dk >= 16 && dk <= 128 && dk % 16 == 0 && group >= 1 && group <= 16 &&
+           page_size >= 16 && page_size % 16 == 0;
+}
+
+// rows: int32 [num_rows], the flat tokens to compute (each its request's only token of the step).
+extern "C" int ti_attn_bias_decode(const void* q, const int* rows, int num_rows, const int* positions,
+                                   const int* req_of_tok, const int* block_table, int bt_stride,
+                                   const void* pages, int num_pages, int page_size, int num_heads,
+                                   int num_kv_heads, int head_dim, int window, int keep_first, float scale,
+                                   const float* dist_bias, int n_dist, const float* gate, int gate_stride,
+                                   void* out, int* status, void* stream) {
+    if (num_rows == 0) return 0;
+    TI_REQUIRE(num_heads % num_kv_heads == 0, "attn_bias_decode: %d heads over %d kv heads", num_heads, num_kv_heads);
+    TI_REQUIRE(ti_attn_bias_decode_supported(head_dim, head_dim, num_heads / num_kv_heads, page_size),
+               "attn_bias_decode: head_dim %d, %d heads per kv head or page size %d is not supported",
+               head_dim, num_heads / num_kv_heads, page_size);
+    TI_REQUIRE(num_kv_heads <= 65535, "attn_bias_decode: %d kv heads exceed the grid limit", num_kv_heads);
+    TI_REQUIRE(dist_bias != nullptr && n_dist >= 1 && rows != nullptr, "attn_bias_decode: no bias table or no rows");
+#define CASE(HD)                                                                                      \
+    case HD:                                                                                          \
+        return launch_decode<HD>((const bf16*)q, rows, num_rows, positions, req_of_tok, block_table,   \
+                                 bt_stride, (const bf16*)pages, num_pages, page_size, num_heads,       \
+                                 num_kv_heads, window, keep_first, scale, dist_bias, n_dist, gate,     \
+                                 gate_stride, (bf16*)out, status, (cudaStream_t)stream)
+    switch (head_dim) {
+        CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
+    }
+#undef CASE
+    return ti_fail("attn_bias_decode: head_dim %d", head_dim);
 }

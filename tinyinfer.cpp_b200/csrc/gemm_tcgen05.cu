@@ -54,7 +54,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ qkv::Epilogue qkv_e, float* __restrict__ c,
                     bf16* __restrict__ out_act, int m, int n, int k, int ldc, int ld_act, int mode,
-                    float* __restrict__ ws, int splits, int* __restrict__ status) {
+                    float* __restrict__ ws, int splits, int* __restrict__ status,
+                    const int* __restrict__ group_of_tile, const int* __restrict__ tiles_m_dev) {
     using T = Tile<BN>;
     constexpr int STAGES = T::STAGES;
     extern __shared__ unsigned char smem_raw[];
@@ -70,7 +71,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (k + BK - 1) / BK;
-    const int tiles_m = (m + BM - 1) / BM, tiles_n = (n + BN - 1) / BN;
+    // Grouped: the rows of A fall into groups, each a whole number of 128-row tiles with a weight
+    // matrix of its own (w holds the groups' [n, k] matrices one after the other);
+    // `group_of_tile[i]` names the group of row tile i, and the number of row tiles comes from the
+    // device (the kernel before decided it), so such a launch is not a dependent one.
+    int tiles_m = (m + BM - 1) / BM;
+    if (tiles_m_dev != nullptr) {
+        tiles_m = *tiles_m_dev;
+        m = tiles_m * BM;
+    }
+    const int tiles_n = (n + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
     // a work unit: tile unit / splits, k blocks [num_kb * r / splits, num_kb * (r + 1) / splits) for r = unit % splits
     const int num_units = num_tiles * splits;
@@ -100,7 +110,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int primed = 0;
             for (int unit = blockIdx.x; unit < num_units && primed < STAGES; unit += gridDim.x) {
                 const Unit u = unit_of(unit, splits, num_kb);
-                const int n0 = (u.tile / tiles_m) * BN;
+                const int n0 = (u.tile / tiles_m) * BN + (group_of_tile ? group_of_tile[u.tile % tiles_m] * n : 0);
                 for (int kb = u.kb_begin; kb < u.kb_end && primed < STAGES; ++kb, ++primed) {
                     mbar_expect_tx(&full[primed], T::STAGE_A + T::STAGE_B);
                     tma_load_2d(stage_b + primed * T::STAGE_B, &map_w, &full[primed], kb * BK, n0);
@@ -110,7 +120,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int it = 0;
             for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
                 const Unit u = unit_of(unit, splits, num_kb);
-                const int m0 = (u.tile % tiles_m) * BM, n0 = (u.tile / tiles_m) * BN;
+                const int m0 = (u.tile % tiles_m) * BM;
+                const int n0 = (u.tile / tiles_m) * BN + (group_of_tile ? group_of_tile[u.tile % tiles_m] * n : 0);
                 for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= primed) {
@@ -364,17 +375,17 @@ int launch_tiles(const void* a, const void* w, const qkv::Epilogue& e, float* c,
         const int tiles = tiles_m * ((n + 255) / 256) * splits;
         ti_launch_pdl(gemm_tcgen05_kernel<256>, tiles < sms ? tiles : sms, THREADS, Tile<256>::SMEM,
                       (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, ws,
-                      splits, status);
+                      splits, status, (const int*)nullptr, (const int*)nullptr);
     } else if (width == 128) {
         const int tiles = tiles_m * ((n + 127) / 128) * splits;
         ti_launch_pdl(gemm_tcgen05_kernel<128>, tiles < sms ? tiles : sms, THREADS, Tile<128>::SMEM,
                       (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, ws,
-                      splits, status);
+                      splits, status, (const int*)nullptr, (const int*)nullptr);
     } else {
         const int tiles = tiles_m * ((n + 63) / 64) * splits;
         ti_launch_pdl(gemm_tcgen05_kernel<64>, tiles < sms ? tiles : sms, THREADS, Tile<64>::SMEM,
                       (cudaStream_t)stream, map_a, map_w, e, c, (bf16*)out_act, m, n, k, ldc, ld_act, mode, ws,
-                      splits, status);
+                      splits, status, (const int*)nullptr, (const int*)nullptr);
     }
     if (int rc = ti_check_launch("gemm_tcgen05")) return rc;
     if (splits > 1 && add_runs) {
@@ -446,6 +457,53 @@ extern "C" int ti_gemm_tcgen05(const void* a, const void* w, float* c, void* out
     const int width = tiles_m * ((n + 255) / 256) >= sms ? 256 : tiles_m * ((n + 127) / 128) * 2 >= sms ? 128 : 64;
     return launch_tiles(a, w, qkv::Epilogue{}, c, out_act, m, n, k, lda, ldw, ldc, ld_act, mode, width, nullptr, 1,
                         status, stream);
+}
+
+// Grouped product: row tile i (128 rows of a) is multiplied by the i-th named group's weights,
+// w + group_of_tile[i] * n * ldw; `tiles_m_dev` (device) says how many row tiles there are, at most
+// m_max / 128.  c (MODE_STORE) or out_act (MODE_SWIGLU) has m_max rows.  Not a dependent launch.
+extern "C" int ti_gemm_tcgen05_grouped(const void* a, const void* w, float* c, void* out_act, int m_max, int n,
+                                       int k, int lda, int ldw, int ldc, int ld_act, int mode, int groups,
+                                       const int* group_of_tile, const int* tiles_m_dev, int* status,
+                                       void* stream) {
+    if (m_max == 0 || n == 0) return 0;
+    TI_REQUIRE(mode == MODE_STORE || mode == MODE_SWIGLU, "gemm_tcgen05_grouped: mode %d", mode);
+    TI_REQUIRE(m_max % BM == 0 && ti_gemm_tcgen05_supported(m_max, n, k, lda, ldw, ldc, mode),
+               "gemm_tcgen05_grouped: rows %d must be a multiple of %d, K=%d and the row strides multiples "
+               "of 8, N=%d a multiple of 4 (16 with SwiGLU)", m_max, BM, k, n);
+    TI_REQUIRE((uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0 && group_of_tile != nullptr && tiles_m_dev != nullptr,
+               "gemm_tcgen05_grouped: operands must be 16-byte aligned and the tile list given");
+    TI_REQUIRE(mode == MODE_SWIGLU ? ((uintptr_t)out_act % 16 == 0 && ld_act % 8 == 0) : (uintptr_t)c % 16 == 0,
+               "gemm_tcgen05_grouped: the output must be 16-byte aligned");
+    int device = 0, sms = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int tiles_m = m_max / BM;
+    CUtensorMap map_a, map_w;
+    if (int rc = make_map_bf16(&map_a, a, m_max, k, lda, BM, "gemm_tcgen05_grouped")) return rc;
+    const int width = tiles_m * ((n + 255) / 256) >= sms ? 256 : 128;
+    if (int rc = make_map_bf16(&map_w, w, (long long)groups * n, k, ldw, width, "gemm_tcgen05_grouped")) return rc;
+    static TiPerDevice configured;
+    if (configured.first_use()) {
+        cudaError_t e2 = cudaFuncSetAttribute(gemm_tcgen05_kernel<256>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, Tile<256>::SMEM);
+        if (e2 == cudaSuccess)
+            e2 = cudaFuncSetAttribute(gemm_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Tile<128>::SMEM);
+        if (e2 != cudaSuccess) return ti_fail("gemm_tcgen05_grouped: %s", cudaGetErrorString(e2));
+        configured.mark();
+    }
+    const int tiles = tiles_m * ((n + width - 1) / width);
+    const int grid = tiles < sms ? tiles : sms;
+    if (width == 256)
+        gemm_tcgen05_kernel<256><<<grid, THREADS, Tile<256>::SMEM, (cudaStream_t)stream>>>(
+            map_a, map_w, qkv::Epilogue{}, c, (bf16*)out_act, m_max, n, k, ldc, ld_act, mode, nullptr, 1, status,
+            group_of_tile, tiles_m_dev);
+    else
+        gemm_tcgen05_kernel<128><<<grid, THREADS, Tile<128>::SMEM, (cudaStream_t)stream>>>(
+            map_a, map_w, qkv::Epilogue{}, c, (bf16*)out_act, m_max, n, k, ldc, ld_act, mode, nullptr, 1, status,
+            group_of_tile, tiles_m_dev);
+    return ti_check_launch("gemm_tcgen05_grouped");
 }
 
 // The QKV product of a prompt portion with the epilogue of qkv_epilogue.cuh (head size 128), on

@@ -11,6 +11,11 @@
 //     block; the float32 result goes to the pair's own row of a scratch.
 //  4. moe_combine: residual[t] += the rows of t's pairs, in slot order.
 //
+// Steps of very many tokens take the tcgen05 product of gemm_tcgen05.cu in its grouped form
+// instead of 2 and 3; this file then brings what surrounds it: moe_sort_padded (every expert's
+// pairs padded to whole tiles of 128 rows), moe_gather_scaled (the rows of h times their weights,
+// in that order) and moe_combine_rows.
+//
 // No atomics touch a result, so a row's bits depend on its own operands only.  K is walked in
 // steps of 32 through a three-stage cp.async ring; warps are arranged 2 x 2 over a 64 x 128
 // tile of products (GATED: 64 gate and 64 up columns, interleaved in runs of 32 so that a warp
@@ -86,7 +91,7 @@ template <bool GATED>
 __global__ void __launch_bounds__(THREADS)
 moe_grouped_kernel(const bf16* a, int lda, const int* __restrict__ sorted_slot,
                    const int* __restrict__ tiles, const int* __restrict__ meta, int top,
-                   const bf16* __restrict__ w0, const bf16* __restrict__ w1, int n, int k,
+                   const bf16* __restrict__ w0, int interleaved, int n, int k,
                    const float* __restrict__ weights, bf16* __restrict__ y_sorted,
                    float* __restrict__ out_rows) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -107,8 +112,8 @@ moe_grouped_kernel(const bf16* a, int lda, const int* __restrict__ sorted_slot,
         row_src[r] = src;
     }
     __syncthreads();
-    const bf16* wg = w0 + (size_t)expert * n * k;
-    const bf16* wu = GATED ? w1 + (size_t)expert * n * k : nullptr;
+    // GATED: the expert's 2n rows (strips of 8 gate rows and their 8 up rows, or gate rows then up rows)
+    const bf16* wg = w0 + (size_t)expert * (GATED ? 2 : 1) * n * k;
 
     // the weight row behind row r of the stage's B part
     auto b_row = [&](int r) -> const bf16* {
@@ -116,7 +121,9 @@ moe_grouped_kernel(const bf16* a, int lda, const int* __restrict__ sorted_slot,
             const int half = r >> 6, in = r & 63;
             const int col = n0 + half * 32 + (in & 31);
             if (col >= n) return nullptr;
-            return (in < 32 ? wg : wu) + (size_t)col * k;
+            const size_t gate_row = interleaved ? (size_t)(col >> 3) * 16 + (col & 7) : (size_t)col;
+            const size_t row = in < 32 ? gate_row : (interleaved ? gate_row + 8 : (size_t)n + col);
+            return wg + row * k;
         }
         const int col = n0 + r;
         return col < n ? wg + (size_t)col * k : nullptr;
@@ -220,7 +227,108 @@ __global__ void moe_combine_kernel(const float* __restrict__ rows, int top, int 
     residual[(size_t)t * res_stride + c] += total;
 }
 
+// For the grouped tcgen05 product: every expert's pairs padded to whole tiles of 128 rows.
+// row_pair[row] = pair behind a row (-1: padding), pos_of_pair[pair] = its row,
+// group_of_tile[i] = expert of row tile i, tiles_m[0] = number of row tiles.
+__global__ void __launch_bounds__(1024)
+moe_sort_padded_kernel(const int* __restrict__ ids, int n_pairs, int experts, int max_rows,
+                       int* __restrict__ row_pair, int* __restrict__ pos_of_pair,
+                       int* __restrict__ group_of_tile, int* __restrict__ tiles_m) {
+    extern __shared__ int sh[];
+    int* counts = sh;
+    int* offsets = sh + experts;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+    for (int r = threadIdx.x; r < max_rows; r += blockDim.x) row_pair[r] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < experts) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, nt = 0;
+        for (int e = 0; e < experts; ++e) {
+            offsets[e] = at;
+            const int t = (counts[e] + 127) / 128;
+            for (int r = 0; r < t; ++r) group_of_tile[nt++] = e;
+            at += t * 128;
+            counts[e] = 0;
+        }
+        tiles_m[0] = nt;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = ids[i];
+        if (e < 0 || e >= experts) continue;
+        const int pos = offsets[e] + atomicAdd(&counts[e], 1);
+        row_pair[pos] = i;
+        pos_of_pair[i] = pos;
+    }
+}
+
+// a[row] = bfloat16(w * h[token]) for the pair behind the row, zeros for padding; 8 elements a thread
+__global__ void moe_gather_scaled_kernel(const bf16* __restrict__ h, int h_stride, const int* __restrict__ row_pair,
+                                         const int* __restrict__ tiles_m, const float* __restrict__ weights,
+                                         int top, int width, bf16* __restrict__ a) {
+    const int row = blockIdx.x;
+    if (row >= tiles_m[0] * 128) return;
+    const int pair = row_pair[row];
+    const float w = pair >= 0 ? weights[pair] : 0.0f;
+    const bf16* src = h + (size_t)(pair >= 0 ? pair / top : 0) * h_stride;
+    for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (pair >= 0) {
+            v = *reinterpret_cast<const uint4*>(src + c);
+            __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(p[i]);
+                p[i] = __floats2bfloat162_rn(f.x * w, f.y * w);
+            }
+        }
+        *reinterpret_cast<uint4*>(a + (size_t)row * width + c) = v;
+    }
+}
+
+__global__ void moe_combine_rows_kernel(const float* __restrict__ rows, const int* __restrict__ pos_of_pair, int top,
+                                        int width, int num_tokens, float* __restrict__ residual, int res_stride) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)num_tokens * width) return;
+    const int t = (int)(i / width), c = (int)(i % width);
+    float total = 0.0f;
+    for (int s = 0; s < top; ++s) total += rows[(size_t)pos_of_pair[t * top + s] * width + c];
+    residual[(size_t)t * res_stride + c] += total;
+}
+
 }  // namespace
+
+// The pieces around the grouped tcgen05 product.  max_rows = (pairs / 128 + experts) * 128.
+extern "C" int ti_moe_sort_padded(const int* ids, int num_pairs, int experts, int max_rows, int* row_pair,
+                                  int* pos_of_pair, int* group_of_tile, int* tiles_m, void* stream) {
+    TI_REQUIRE(experts >= 1 && experts <= 4096, "moe_sort_padded: %d experts", experts);
+    moe_sort_padded_kernel<<<1, 1024, 2 * experts * sizeof(int), (cudaStream_t)stream>>>(
+        ids, num_pairs, experts, max_rows, row_pair, pos_of_pair, group_of_tile, tiles_m);
+    return ti_check_launch("moe_sort_padded");
+}
+
+extern "C" int ti_moe_gather_scaled(const void* h, int h_stride, const int* row_pair, const int* tiles_m,
+                                    const float* weights, int top, int width, int max_rows, void* a, void* stream) {
+    TI_REQUIRE(width % 8 == 0 && h_stride % 8 == 0 && ((uintptr_t)h) % 16 == 0 && ((uintptr_t)a) % 16 == 0,
+               "moe_gather_scaled: rows must be 16-byte aligned");
+    if (max_rows == 0) return 0;
+    moe_gather_scaled_kernel<<<max_rows, 128, 0, (cudaStream_t)stream>>>((const bf16*)h, h_stride, row_pair, tiles_m,
+                                                                        weights, top, width, (bf16*)a);
+    return ti_check_launch("moe_gather_scaled");
+}
+
+extern "C" int ti_moe_combine_rows(const float* rows, const int* pos_of_pair, int top, int width, int num_tokens,
+                                   float* residual, int res_stride, void* stream) {
+    const size_t total = (size_t)num_tokens * width;
+    if (total == 0) return 0;
+    moe_combine_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        rows, pos_of_pair, top, width, num_tokens, residual, res_stride);
+    return ti_check_launch("moe_combine_rows");
+}
 
 extern "C" int ti_moe_grouped_supported(int width, int ff, int experts) {
     return width % 32 == 0 && ff % 32 == 0 && experts >= 1 && experts <= 4096;
@@ -228,7 +336,7 @@ extern "C" int ti_moe_grouped_supported(int width, int ff, int experts) {
 
 // Scratch the caller brings: sorted_slot int32 [pairs], tiles int32 [(pairs / 64 + experts) * 3],
 // meta int32 [1], y_sorted bfloat16 [pairs, ff], out_rows float32 [pairs, width].
-extern "C" int ti_moe_grouped(const void* h, int h_stride, const void* w_gate, const void* w_up,
+extern "C" int ti_moe_grouped(const void* h, int h_stride, const void* w_gate_up, int interleaved,
                               const void* w_down, const int* ids, const float* weights, int num_tokens,
                               int top, int experts, int width, int ff, int* sorted_slot, int* tiles,
                               int* meta, void* y_sorted, float* out_rows, float* residual,
@@ -252,11 +360,11 @@ extern "C" int ti_moe_grouped(const void* h, int h_stride, const void* w_gate, c
     }
     dim3 g1((ff + BNW / 2 - 1) / (BNW / 2), max_tiles);
     moe_grouped_kernel<true><<<g1, THREADS, SMEM, s>>>(
-        (const bf16*)h, h_stride, sorted_slot, tiles, meta, top, (const bf16*)w_gate, (const bf16*)w_up, ff, width,
+        (const bf16*)h, h_stride, sorted_slot, tiles, meta, top, (const bf16*)w_gate_up, interleaved, ff, width,
         weights, (bf16*)y_sorted, nullptr);
     dim3 g2((width + BNW - 1) / BNW, max_tiles);
     moe_grouped_kernel<false><<<g2, THREADS, SMEM, s>>>(
-        (const bf16*)y_sorted, ff, sorted_slot, tiles, meta, top, (const bf16*)w_down, nullptr, width, ff,
+        (const bf16*)y_sorted, ff, sorted_slot, tiles, meta, top, (const bf16*)w_down, 0, width, ff,
         nullptr, nullptr, out_rows);
     const size_t total = (size_t)num_tokens * width;
     moe_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(out_rows, top, width, num_tokens,

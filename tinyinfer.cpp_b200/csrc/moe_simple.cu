@@ -5,7 +5,8 @@
 //    sigmoid of their logits as weights; one more column of the same product, if there is one,
 //    becomes the sigmoid gate of a shared expert.
 //  * moe_gate_up_simple: y[t][s] = silu(w g) * (w u) with g = Wgate_e h_t, u = Wup_e h_t, e and w
-//    the expert and weight of the token's slot s.  The weight stands for a scaling of the
+//    the expert and weight of the token's slot s (an expert's gate and up rows are stacked in one
+//    matrix, interleaved in strips of 8 or one after the other).  The weight stands for a scaling of the
 //    expert's input: (Wgate (w h), Wup (w h)) = (w g, w u).
 //  * moe_down_simple: out[t] += sum over the slots, in order, of Wdown_e y[t][s].
 //  * scale_rows: y[t] *= f[t].
@@ -59,8 +60,8 @@ router_topk_kernel(const float* logits, int stride, int num_tokens, int experts,
 // one warp per output element f of one (token, slot)
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(WARPS * 32)
-moe_gate_up_simple_kernel(const TA* __restrict__ h, int h_stride, const TW* __restrict__ w_gate,
-                          const TW* __restrict__ w_up, const int* __restrict__ ids,
+moe_gate_up_simple_kernel(const TA* __restrict__ h, int h_stride, const TW* __restrict__ w_gate_up,
+                          int interleaved, const int* __restrict__ ids,
                           const float* __restrict__ weights, int top, int width, int ff,
                           TA* __restrict__ y) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -70,8 +71,11 @@ moe_gate_up_simple_kernel(const TA* __restrict__ h, int h_stride, const TW* __re
     const int e = ids[ts];
     const float w = weights[ts];
     const TA* x = h + (size_t)(ts / top) * h_stride;
-    const TW* wg = w_gate + ((size_t)e * ff + f) * width;
-    const TW* wu = w_up + ((size_t)e * ff + f) * width;
+    // an expert's 2 ff rows: strips of 8 gate rows and their 8 up rows, or all gate rows and then all up rows
+    const size_t gate_row = interleaved ? (size_t)(f >> 3) * 16 + (f & 7) : (size_t)f;
+    const size_t up_row = interleaved ? gate_row + 8 : (size_t)ff + f;
+    const TW* wg = w_gate_up + ((size_t)e * 2 * ff + gate_row) * width;
+    const TW* wu = w_gate_up + ((size_t)e * 2 * ff + up_row) * width;
     float g = 0.0f, u = 0.0f;
     for (int k = lane; k < width; k += 32) {
         const float xv = to_f32(x[k]);
@@ -134,8 +138,8 @@ extern "C" int ti_router_topk(const float* logits, int stride, int num_tokens, i
     return ti_check_launch("router_topk");
 }
 
-extern "C" int ti_moe_gate_up_simple(const void* h, int act_dtype, int h_stride, const void* w_gate,
-                                     const void* w_up, int w_dtype, const int* ids,
+extern "C" int ti_moe_gate_up_simple(const void* h, int act_dtype, int h_stride, const void* w_gate_up,
+                                     int interleaved, int w_dtype, const int* ids,
                                      const float* weights, int num_tokens, int top, int width, int ff,
                                      void* y, void* stream) {
     if (num_tokens == 0) return 0;
@@ -143,7 +147,7 @@ extern "C" int ti_moe_gate_up_simple(const void* h, int act_dtype, int h_stride,
     cudaStream_t s = (cudaStream_t)stream;
 #define CALL(TA, TW)                                                                         \
     moe_gate_up_simple_kernel<TA, TW><<<grid, WARPS * 32, 0, s>>>(                            \
-        (const TA*)h, h_stride, (const TW*)w_gate, (const TW*)w_up, ids, weights, top, width, ff, (TA*)y)
+        (const TA*)h, h_stride, (const TW*)w_gate_up, interleaved, ids, weights, top, width, ff, (TA*)y)
     TI_DISPATCH_AW(act_dtype, w_dtype, CALL)
 #undef CALL
     return ti_check_launch("moe_gate_up_simple");

@@ -130,6 +130,7 @@ class CudaOps:
         self._gated = None
         self.use_tc_biased_attention = True   # tensor-core prompt kernel of the attention with a distance bias
         self.grouped_experts_from = 128       # (token, slot) pairs from which the experts run as grouped products
+        self.tcgen05_experts_from = 1024      # ... and from which those products run on tcgen05
         self._counters = None
         self.use_tc_attention = True      # tcgen05 prompt attention where the shape allows
         self.use_2sm_gemm = True          # pairs of SMs for products with enough 256 x 256 tiles
@@ -205,7 +206,7 @@ class CudaOps:
         c.ti_attention_bias_simple.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
                                                _i, _i, _i, _i, _f, _vp, _i, _vp, _i, _vp, _vp, _vp]
         c.ti_router_topk.argtypes = [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]
-        c.ti_moe_gate_up_simple.argtypes = [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp]
+        c.ti_moe_gate_up_simple.argtypes = [_vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp]
         c.ti_moe_down_simple.argtypes = [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _vp]
         c.ti_scale_rows.argtypes = [_vp, _i, _i, _vp, _i, _i, _vp]
 
@@ -238,6 +239,8 @@ class CudaOps:
             b.ti_gemm_tcgen05_add_runs.argtypes = [_vp, _vp, _i, _i, _i, _i, _i, _vp]
             b.ti_gemm_tcgen05_splits.argtypes = [_i, _i, _i, _i]
             b.ti_gemm_tcgen05_supported.argtypes = [_i, _i, _i, _i, _i, _i, _i]
+            b.ti_gemm_tcgen05_grouped.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp,
+                                                  _vp, _vp]
             b.ti_gemm_tcgen05_2sm.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
             qkv_args = [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i,
                         _i, _i, _vp, _vp, _vp]
@@ -268,9 +271,15 @@ class CudaOps:
             b.ti_attn_bias_prefill_supported.argtypes = [_i, _i, _i]
             b.ti_attn_bias_prefill.argtypes = [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f,
                                                _vp, _i, _vp, _i, _vp, _vp, _vp]
+            b.ti_attn_bias_decode_supported.argtypes = [_i, _i, _i, _i]
+            b.ti_attn_bias_decode.argtypes = [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f,
+                                              _vp, _i, _vp, _i, _vp, _vp, _vp]
             b.ti_moe_grouped_supported.argtypes = [_i, _i, _i]
-            b.ti_moe_grouped.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp,
+            b.ti_moe_grouped.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp,
                                          _vp, _vp, _i, _vp]
+            b.ti_moe_sort_padded.argtypes = [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]
+            b.ti_moe_gather_scaled.argtypes = [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp]
+            b.ti_moe_combine_rows.argtypes = [_vp, _vp, _i, _i, _i, _vp, _i, _vp]
             self._gated = b
         return self._gated
 
@@ -899,6 +908,17 @@ class CudaOps:
                 n_rows = rows.shape[0]
                 if n_rows == 0:
                     return
+            single = lists["single_rows"]
+            if single.shape[0] and self.gated.ti_attn_bias_decode_supported(
+                    dk, dv, num_heads // num_kv_heads, cache.page_size):
+                self._ok(self.gated.ti_attn_bias_decode(
+                    q.data_ptr(), single.data_ptr(), single.shape[0], step.positions.data_ptr(),
+                    step.req_of_tok.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(), pages.shape[0],
+                    cache.page_size, num_heads, num_kv_heads, dk, int(window or 0), int(keep_first),
+                    float(scale), dist_bias.data_ptr(), dist_bias.shape[1], _ptr(gate),
+                    gate.stride(0) if gate is not None else 0, out.data_ptr(), self.status.data_ptr(),
+                    self._stream()), self.gated)
+                return
         self._ok(self.core.ti_attention_bias_simple(
             q.data_ptr(), _code(q, "q"), _ptr(rows), step.positions.data_ptr(), step.req_of_tok.data_ptr(),
             bt.data_ptr(), bt.stride(0), pages.data_ptr(), _code(pages, "cache"), pages.shape[0],
@@ -910,10 +930,18 @@ class CudaOps:
     # ---- routed feed-forward ---------------------------------------------------------------
     def pack_experts(self, gate, up, down):
         """The stacked weights of a routed feed-forward (``[experts, ff, width]`` twice and
-        ``[experts, width, ff]``) in the layout the kernels want."""
+        ``[experts, width, ff]``) in the layout the kernels want: an expert's gate and up rows as
+        one matrix (strips of 8 and 8 where the sizes allow, for the SwiGLU epilogues)."""
         _need(gate.dtype == up.dtype == down.dtype, "pack_experts: one dtype for all experts")
         _code(gate, "pack_experts")
-        return {"gate": gate.contiguous(), "up": up.contiguous(), "down": down.contiguous()}
+        experts, ff, width = gate.shape
+        interleaved = gate.dtype == torch.bfloat16 and ff % 8 == 0
+        if interleaved:          # strips of 8 gate rows and their 8 up rows, as pack_gate_up lays them out
+            gate_up = torch.stack([gate.view(experts, ff // 8, 8, width), up.view(experts, ff // 8, 8, width)], dim=2)
+            gate_up = gate_up.reshape(experts, 2 * ff, width).contiguous()
+        else:
+            gate_up = torch.cat([gate, up], dim=1).contiguous()
+        return {"gate_up": gate_up, "down": down.contiguous(), "interleaved": interleaved}
 
     def router_topk(self, logits, experts, top, ids, weights, shared_gate=None):
         """Per row the ``top`` largest of the first ``experts`` logits (ties: the lower index):
@@ -934,22 +962,53 @@ class CudaOps:
         u = Wup_e h[t], e = ids[t, s], w = weights[t, s]."""
         t, width = h.shape
         top = ids.shape[1]
-        experts, ff, _ = w["gate"].shape
-        _need(w["gate"].shape == w["up"].shape == (experts, ff, width) and w["down"].shape == (experts, width, ff),
+        experts, ff = w["down"].shape[0], w["down"].shape[2]
+        gate_up, interleaved = w["gate_up"], int(w["interleaved"])
+        _need(gate_up.shape == (experts, 2 * ff, width) and w["down"].shape == (experts, width, ff),
               "routed_experts: expert shapes do not agree")
         _need(residual.dtype == torch.float32 and residual.stride(1) == 1 and tuple(residual.shape) == (t, width),
               "routed_experts: float32 residual")
         _need(h.stride(1) == 1, "routed_experts: rows must be contiguous")
         if (self.grouped_experts_from is not None and t * top >= self.grouped_experts_from
-                and h.dtype == torch.bfloat16 and w["gate"].dtype == torch.bfloat16
+                and h.dtype == torch.bfloat16 and gate_up.dtype == torch.bfloat16
                 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
                 and self.gated.ti_moe_grouped_supported(width, ff, experts)):
             pairs = t * top
+            if (self.tcgen05_experts_from is not None and pairs >= self.tcgen05_experts_from and interleaved
+                    and ff % 16 == 0 and width % 8 == 0):
+                # every expert's pairs in whole tiles of 128 rows, the rows of h times their weights
+                # gathered in that order, two grouped tcgen05 products (the first with SwiGLU in its
+                # epilogue), and the pairs' rows added per token
+                max_rows = (pairs // 128 + experts) * 128
+                ints = torch.empty(max_rows + pairs + max_rows // 128 + 1, dtype=torch.int32, device=h.device)
+                row_pair, pos_of_pair = ints[:max_rows], ints[max_rows:max_rows + pairs]
+                group_of_tile, tiles_m = ints[max_rows + pairs:-1], ints[-1:]
+                g = self.gated
+                self._ok(g.ti_moe_sort_padded(ids.data_ptr(), pairs, experts, max_rows, row_pair.data_ptr(),
+                                              pos_of_pair.data_ptr(), group_of_tile.data_ptr(), tiles_m.data_ptr(),
+                                              self._stream()), g)
+                a = torch.empty((max_rows, width), dtype=torch.bfloat16, device=h.device)
+                self._ok(g.ti_moe_gather_scaled(h.data_ptr(), h.stride(0), row_pair.data_ptr(), tiles_m.data_ptr(),
+                                                weights.data_ptr(), top, width, max_rows, a.data_ptr(),
+                                                self._stream()), g)
+                y = torch.empty((max_rows, ff), dtype=torch.bfloat16, device=h.device)
+                self._ok(self.bf16.ti_gemm_tcgen05_grouped(
+                    a.data_ptr(), gate_up.data_ptr(), None, y.data_ptr(), max_rows, 2 * ff, width, width, width, 0,
+                    ff, 2, experts, group_of_tile.data_ptr(), tiles_m.data_ptr(), self.status.data_ptr(),
+                    self._stream()), self.bf16)
+                out_rows = torch.empty((max_rows, width), dtype=torch.float32, device=h.device)
+                self._ok(self.bf16.ti_gemm_tcgen05_grouped(
+                    y.data_ptr(), w["down"].data_ptr(), out_rows.data_ptr(), None, max_rows, width, ff, ff, ff,
+                    width, 0, 0, experts, group_of_tile.data_ptr(), tiles_m.data_ptr(), self.status.data_ptr(),
+                    self._stream()), self.bf16)
+                self._ok(g.ti_moe_combine_rows(out_rows.data_ptr(), pos_of_pair.data_ptr(), top, width, t,
+                                               residual.data_ptr(), residual.stride(0), self._stream()), g)
+                return
             ints = torch.empty(pairs + 3 * (pairs // 64 + experts) + 1, dtype=torch.int32, device=h.device)
             y_sorted = torch.empty((pairs, ff), dtype=torch.bfloat16, device=h.device)
             out_rows = torch.empty((pairs, width), dtype=torch.float32, device=h.device)
             self._ok(self.gated.ti_moe_grouped(
-                h.data_ptr(), h.stride(0), w["gate"].data_ptr(), w["up"].data_ptr(), w["down"].data_ptr(),
+                h.data_ptr(), h.stride(0), gate_up.data_ptr(), interleaved, w["down"].data_ptr(),
                 ids.data_ptr(), weights.data_ptr(), t, top, experts, width, ff, ints.data_ptr(),
                 ints[pairs:].data_ptr(), ints[ints.shape[0] - 1:].data_ptr(), y_sorted.data_ptr(),
                 out_rows.data_ptr(), residual.data_ptr(), residual.stride(0), self._stream()), self.gated)
@@ -957,8 +1016,8 @@ class CudaOps:
             return
         y = torch.empty((t, top, ff), dtype=h.dtype, device=h.device)
         self._ok(self.core.ti_moe_gate_up_simple(
-            h.data_ptr(), _code(h, "routed_experts"), h.stride(0), w["gate"].data_ptr(), w["up"].data_ptr(),
-            _code(w["gate"], "routed_experts"), ids.data_ptr(), weights.data_ptr(), t, top, width, ff,
+            h.data_ptr(), _code(h, "routed_experts"), h.stride(0), gate_up.data_ptr(), interleaved,
+            _code(gate_up, "routed_experts"), ids.data_ptr(), weights.data_ptr(), t, top, width, ff,
             y.data_ptr(), self._stream()))
         self._ok(self.core.ti_moe_down_simple(
             y.data_ptr(), _code(y, "routed_experts"), w["down"].data_ptr(), _code(w["down"], "routed_experts"),
