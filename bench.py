@@ -537,6 +537,9 @@ def design_arm(args) -> int:
             pff, dff = per_layer(spans, "ffn") + extra, per_layer(dspans, "ffn") + dextra
             a["per_layer_us"] = {"prompt_attention": round(pa * 1e3, 1), "decode_attention": round(da * 1e3, 1),
                                  "prompt_ffn": round(pff * 1e3, 1), "decode_ffn": round(dff * 1e3, 1)}
+            a["calls_per_layer_us"] = {
+                "prompt": {n: round(sum(v) / layers * 1e3, 1) for n, v in spans.items()},
+                "decode": {n: round(sum(v) / layers * 1e3, 1) for n, v in dspans.items()}}
             a["roofline_frac"] = {
                 "prompt_attention": round(attn_flops / (pa * 1e-3) / (pk["bf16_tflops"] * 1e12), 3),
                 "decode_attention": round(attn_bytes / (da * 1e-3) / (pk["hbm_gbs"] * 1e9), 3),

@@ -213,6 +213,30 @@ def test_one_key_carries_the_weight_at_every_edge(ops, where, dtype):
         assert bool(hit) == seen, f"key {target} seen from {last}: expected {'visible' if seen else 'hidden'}"
 
 
+@pytest.mark.parametrize("window, keep", [(0, 0), (2500, 7), (1000, 40)])
+def test_single_rows_with_their_keys_cut_into_runs(ops, window, keep):
+    """Few single-token rows with thousands of keys: the walk over the keys is cut into runs, a
+    block each, and a second launch adds them."""
+    heads, kv, d, ps = 8, 2, 64, 16
+    ctx = [3000, 777, 2049]
+    rows, far = 16, 600
+    from tinyinfer_b200.parts.gated_attention import distance_rows
+    step, cache, q, keys, values, bt = _attention_case(heads, kv, d, d, ps, ctx, [1, 1, 1], torch.bfloat16, seed=8)
+    _fill_pages(cache, bt, keys, values, kv, d, d)
+    rel = torch.randn((rows, heads), generator=torch.Generator().manual_seed(2))
+    dist = rel[torch.tensor(distance_rows(rows, far))].t().contiguous().to(DEV)
+    gate = torch.randn((3, heads * d), generator=torch.Generator().manual_seed(3)).to(DEV)
+    out = torch.empty((3, heads * d), dtype=torch.bfloat16, device=DEV)
+    qd = q.reshape(3, heads * d).to(torch.bfloat16).to(DEV)
+    ops.biased_attention(qd, step, cache, out, heads, kv, d, d, window or None, keep, 0.2, dist, gate)
+    ops.check_status()
+    for r, c in enumerate(ctx):
+        want = plain.attend(q[r:r + 1].bfloat16().double(), keys[r].bfloat16().double(), values[r].bfloat16().double(),
+                            rel.double(), heads // kv, 0.2, window or 10 ** 9, keep, far, c - 1)
+        want = want.reshape(1, heads * d) * torch.sigmoid(gate[r:r + 1].cpu().double())
+        assert (out[r:r + 1].cpu().double() - want).abs().max() < 2e-2 * max(1.0, want.abs().max()), f"row {r}"
+
+
 def test_distance_bias_reaches_the_scores(ops):
     """With equal keys the weights are the softmax of the bias alone: the row of every distance,
     below half the table, in the logarithmic part and beyond the far end."""

@@ -279,7 +279,10 @@ attn_bias_prefill_kernel(const bf16* __restrict__ q, const int* __restrict__ til
 // of the MMA, and the block's four warps take the tiles of 32 keys in turn (tile i of the walk
 // goes to warp i mod 4), each through a two-stage cp.async ring of its own; at the end the warps'
 // partial results meet in shared memory, are added in warp order and gated.  The walk and the
-// mask are those of the prompt kernel; the bias comes straight from the table.
+// mask are those of the prompt kernel; the bias comes straight from the table.  With few rows the
+// walk is cut into `gridDim.z` equal runs, a block each (the count depends on the step's shape
+// alone): a block then leaves its unnormalised sums with their maximum and weight in a scratch,
+// and attn_bias_decode_merge_kernel adds the runs in order, normalises and gates.
 constexpr int DT = 32;
 constexpr int DWARPS = 4;
 
@@ -291,12 +294,14 @@ attn_bias_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows
                         const bf16* __restrict__ pages, int num_pages, int page_size, int num_heads,
                         int num_kv_heads, int window, int keep_first, float scale,
                         const float* __restrict__ dist_bias, int n_dist, const float* gate,
-                        int gate_stride, bf16* __restrict__ out, int* __restrict__ status) {
+                        int gate_stride, bf16* __restrict__ out, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int* __restrict__ status) {
     constexpr int ROW_BYTES = HD * 2 + 16;
     constexpr int CHUNKS = HD / 8;
     constexpr int KSTEPS = HD / 16;
     constexpr int NT_O = HD / 8;
     constexpr int WARP_SMEM = 2 * 2 * DT * ROW_BYTES;
+    const int nsplit = gridDim.z, split = blockIdx.z;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ float sm_m[DWARPS][16], sm_l[DWARPS][16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -309,7 +314,9 @@ attn_bias_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows
     const int lo = window > 0 ? max(0, ctx - window) : 0;
     const int tile_lo = lo / DT, tile_hi = (ctx + DT - 1) / DT;
     const int n_pre = min(tile_lo, (keep_first + DT - 1) / DT);
-    const int n_walk = n_pre + (tile_hi - tile_lo);
+    const int n_all = n_pre + (tile_hi - tile_lo);
+    const int per_split = (n_all + nsplit - 1) / nsplit;
+    const int w_lo = split * per_split, n_walk = min(n_all, w_lo + per_split);   // this block's run of the walk
     auto tile_of = [&](int i) { return i < n_pre ? i : tile_lo + (i - n_pre); };
     unsigned char* mine = smem + (size_t)warp * WARP_SMEM;
 
@@ -345,7 +352,7 @@ attn_bias_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows
         }
     };
 
-    if (warp < n_walk) {
+    if (w_lo + warp < n_walk) {
         unsigned qa[KSTEPS][4];
         const bf16* qbase = q + ((size_t)t * num_heads + (size_t)kvh * group) * HD;
 #pragma unroll
@@ -358,10 +365,10 @@ attn_bias_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows
         }
         const float* bias_r[2] = {dist_bias + (size_t)(kvh * group + min(g, group - 1)) * n_dist,
                                   dist_bias + (size_t)(kvh * group + min(g + 8, group - 1)) * n_dist};
-        issue(tile_of(warp), 0);
+        issue(tile_of(w_lo + warp), 0);
         cp_async_commit();
         int turn = 0;
-        for (int wi = warp; wi < n_walk; wi += DWARPS, ++turn) {
+        for (int wi = w_lo + warp; wi < n_walk; wi += DWARPS, ++turn) {
             const int tile = tile_of(wi);
             const int stage = turn & 1;
             if (wi + DWARPS < n_walk) issue(tile_of(wi + DWARPS), stage ^ 1);
@@ -474,11 +481,39 @@ attn_bias_decode_kernel(const bf16* __restrict__ q, const int* __restrict__ rows
             total += sm_l[w][r] * wt;
             acc += reinterpret_cast<const float*>(smem + (size_t)w * WARP_SMEM)[r * HD + d] * wt;
         }
-        float y = acc / total;
         const int head = kvh * group + r;
+        if (nsplit > 1) {
+            const size_t at = ((size_t)blockIdx.x * num_heads + head) * nsplit + split;
+            part_o[at * HD + d] = acc;
+            if (d == 0) { part_ml[at * 2] = mm; part_ml[at * 2 + 1] = total; }
+            continue;
+        }
+        float y = acc / total;
         if (gate) y *= 1.0f / (1.0f + __expf(-gate[(size_t)t * gate_stride + (size_t)head * HD + d]));
         out[((size_t)t * num_heads + head) * HD + d] = __float2bfloat16_rn(y);
     }
+}
+
+// one block per (row, head), a thread per element: the runs' sums in order
+__global__ void attn_bias_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              const int* __restrict__ rows, int num_heads, int hd, int nsplit,
+                                              const float* gate, int gate_stride, bf16* __restrict__ out) {
+    const int row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    if (d >= hd) return;
+    const int t = rows[row];
+    const size_t at = ((size_t)row * num_heads + head) * nsplit;
+    float mm = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, part_ml[(at + s) * 2]);
+    float total = 0.0f, acc = 0.0f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float m = part_ml[(at + s) * 2];
+        const float wt = m == -INFINITY ? 0.0f : exp2f(m - mm);
+        total += part_ml[(at + s) * 2 + 1] * wt;
+        acc += part_o[(at + s) * hd + d] * wt;
+    }
+    float y = acc / total;
+    if (gate) y *= 1.0f / (1.0f + __expf(-gate[(size_t)t * gate_stride + (size_t)head * hd + d]));
+    out[((size_t)t * num_heads + head) * hd + d] = __float2bfloat16_rn(y);
 }
 
 template <int HD>
@@ -486,7 +521,7 @@ int launch_decode(const bf16* q, const int* rows, int num_rows, const int* posit
                   const int* block_table, int bt_stride, const bf16* pages, int num_pages, int page_size,
                   int num_heads, int num_kv_heads, int window, int keep_first, float scale,
                   const float* dist_bias, int n_dist, const float* gate, int gate_stride, bf16* out,
-                  int* status, cudaStream_t s) {
+                  int nsplit, float* part_o, float* part_ml, int* status, cudaStream_t s) {
     constexpr int SMEM = DWARPS * 2 * 2 * DT * (HD * 2 + 16);
     static TiPerDevice configured;
     if (configured.first_use()) {
@@ -495,11 +530,18 @@ int launch_decode(const bf16* q, const int* rows, int num_rows, const int* posit
         if (e != cudaSuccess) return ti_fail("attn_bias_decode: %s", cudaGetErrorString(e));
         configured.mark();
     }
-    dim3 grid(num_rows, num_kv_heads);
+    dim3 grid(num_rows, num_kv_heads, nsplit);
     attn_bias_decode_kernel<HD><<<grid, DWARPS * 32, SMEM, s>>>(
         q, rows, positions, req_of_tok, block_table, bt_stride, pages, num_pages, page_size, num_heads,
-        num_kv_heads, window, keep_first, scale, dist_bias, n_dist, gate, gate_stride, out, status);
-    return ti_check_launch("attn_bias_decode");
+        num_kv_heads, window, keep_first, scale, dist_bias, n_dist, gate, gate_stride, out, part_o, part_ml,
+        status);
+    if (int rc = ti_check_launch("attn_bias_decode")) return rc;
+    if (nsplit > 1) {
+        attn_bias_decode_merge_kernel<<<dim3(num_rows, num_heads), HD, 0, s>>>(
+            part_o, part_ml, rows, num_heads, HD, nsplit, gate, gate_stride, out);
+        return ti_check_launch("attn_bias_decode_merge");
+    }
+    return 0;
 }
 
 template <int HD>
@@ -569,13 +611,17 @@ extern "C" int ti_attn_bias_decode_supported(int dk, int dv, int group, int page
 }
 
 // rows: int32 [num_rows], the flat tokens to compute (each its request's only token of the step).
+// nsplit > 1: part_o float32 [num_rows, heads, nsplit, head_dim], part_ml float32 [num_rows, heads, nsplit, 2].
 extern "C" int ti_attn_bias_decode(const void* q, const int* rows, int num_rows, const int* positions,
                                    const int* req_of_tok, const int* block_table, int bt_stride,
                                    const void* pages, int num_pages, int page_size, int num_heads,
                                    int num_kv_heads, int head_dim, int window, int keep_first, float scale,
                                    const float* dist_bias, int n_dist, const float* gate, int gate_stride,
-                                   void* out, int* status, void* stream) {
+                                   void* out, int nsplit, float* part_o, float* part_ml, int* status,
+                                   void* stream) {
     if (num_rows == 0) return 0;
+    TI_REQUIRE(nsplit >= 1 && nsplit <= 64 && (nsplit == 1 || (part_o != nullptr && part_ml != nullptr)),
+               "attn_bias_decode: %d runs of keys need a scratch (at most 64)", nsplit);
     TI_REQUIRE(num_heads % num_kv_heads == 0, "attn_bias_decode: %d heads over %d kv heads", num_heads, num_kv_heads);
     TI_REQUIRE(ti_attn_bias_decode_supported(head_dim, head_dim, num_heads / num_kv_heads, page_size),
                "attn_bias_decode: head_dim %d, %d heads per kv head or page size %d is not supported",
@@ -587,7 +633,8 @@ extern "C" int ti_attn_bias_decode(const void* q, const int* rows, int num_rows,
         return launch_decode<HD>((const bf16*)q, rows, num_rows, positions, req_of_tok, block_table,   \
                                  bt_stride, (const bf16*)pages, num_pages, page_size, num_heads,       \
                                  num_kv_heads, window, keep_first, scale, dist_bias, n_dist, gate,     \
-                                 gate_stride, (bf16*)out, status, (cudaStream_t)stream)
+                                 gate_stride, (bf16*)out, nsplit, part_o, part_ml, status,             \
+                                 (cudaStream_t)stream)
     switch (head_dim) {
         CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
     }

@@ -32,14 +32,33 @@ router_topk_kernel(const float* logits, int stride, int num_tokens, int experts,
     const int t = blockIdx.x * WARPS + warp;
     if (t >= num_tokens) return;
     const float* z = logits + (size_t)t * stride;
+    // up to 256 experts: a lane's logits stay in registers, a chosen one is struck out there
+    constexpr int HELD = 8;
+    const bool held = experts <= 32 * HELD;
+    float mine[HELD];
+    bool gone[HELD];
+#pragma unroll
+    for (int i = 0; i < HELD; ++i) {
+        const int e = lane + 32 * i;
+        mine[i] = held && e < experts ? z[e] : 0.0f;
+        gone[i] = !(held && e < experts);
+    }
     for (int s = 0; s < top; ++s) {
         float best = -INFINITY;
         int best_e = experts;                         // larger than every index: loses every tie
-        for (int e = lane; e < experts; e += 32) {
-            bool taken = false;
-            for (int c = 0; c < s; ++c) taken |= chosen[warp][c] == e;
-            const float v = z[e];
-            if (!taken && (v > best || (v == best && e < best_e) || best_e == experts)) { best = v; best_e = e; }
+        if (held) {
+#pragma unroll
+            for (int i = 0; i < HELD; ++i) {
+                const int e = lane + 32 * i;
+                if (!gone[i] && (best_e == experts || mine[i] > best)) { best = mine[i]; best_e = e; }
+            }
+        } else {
+            for (int e = lane; e < experts; e += 32) {
+                bool taken = false;
+                for (int c = 0; c < s; ++c) taken |= chosen[warp][c] == e;
+                const float v = z[e];
+                if (!taken && (v > best || (v == best && e < best_e) || best_e == experts)) { best = v; best_e = e; }
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -47,6 +66,11 @@ router_topk_kernel(const float* logits, int stride, int num_tokens, int experts,
             const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
             if (oe < experts && (best_e == experts || ov > best || (ov == best && oe < best_e))) { best = ov; best_e = oe; }
         }
+        best_e = __shfl_sync(0xffffffffu, best_e, 0);
+        best = __shfl_sync(0xffffffffu, best, 0);
+#pragma unroll
+        for (int i = 0; i < HELD; ++i)
+            if (lane + 32 * i == best_e) gone[i] = true;
         if (lane == 0) {
             chosen[warp][s] = best_e;
             ids[(size_t)t * top + s] = best_e;

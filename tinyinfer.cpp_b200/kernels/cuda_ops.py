@@ -273,7 +273,7 @@ class CudaOps:
                                                _vp, _i, _vp, _i, _vp, _vp, _vp]
             b.ti_attn_bias_decode_supported.argtypes = [_i, _i, _i, _i]
             b.ti_attn_bias_decode.argtypes = [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f,
-                                              _vp, _i, _vp, _i, _vp, _vp, _vp]
+                                              _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp]
             b.ti_moe_grouped_supported.argtypes = [_i, _i, _i]
             b.ti_moe_grouped.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp,
                                          _vp, _vp, _i, _vp]
@@ -911,13 +911,25 @@ class CudaOps:
             single = lists["single_rows"]
             if single.shape[0] and self.gated.ti_attn_bias_decode_supported(
                     dk, dv, num_heads // num_kv_heads, cache.page_size):
+                # few rows: the keys of a row in several runs, a block each, so that the SMs are busy.
+                # The count depends on the step's shape alone (padded rows, the model's bounds).
+                n_single = single.shape[0]
+                most_keys = step.max_position or step.max_ctx_len
+                if window:
+                    most_keys = min(most_keys, int(window) + int(keep_first))
+                nsplit = max(1, min(2 * self.num_sms // max(1, n_single * num_kv_heads), -(-most_keys // 32) // 8, 64))
+                part_o = part_ml = None
+                if nsplit > 1:
+                    part_o = torch.empty((n_single, num_heads, nsplit, dk), dtype=torch.float32, device=q.device)
+                    part_ml = torch.empty((n_single, num_heads, nsplit, 2), dtype=torch.float32, device=q.device)
+                    self.launches += 1
                 self._ok(self.gated.ti_attn_bias_decode(
                     q.data_ptr(), single.data_ptr(), single.shape[0], step.positions.data_ptr(),
                     step.req_of_tok.data_ptr(), bt.data_ptr(), bt.stride(0), pages.data_ptr(), pages.shape[0],
                     cache.page_size, num_heads, num_kv_heads, dk, int(window or 0), int(keep_first),
                     float(scale), dist_bias.data_ptr(), dist_bias.shape[1], _ptr(gate),
-                    gate.stride(0) if gate is not None else 0, out.data_ptr(), self.status.data_ptr(),
-                    self._stream()), self.gated)
+                    gate.stride(0) if gate is not None else 0, out.data_ptr(), nsplit, _ptr(part_o),
+                    _ptr(part_ml), self.status.data_ptr(), self._stream()), self.gated)
                 return
         self._ok(self.core.ti_attention_bias_simple(
             q.data_ptr(), _code(q, "q"), _ptr(rows), step.positions.data_ptr(), step.req_of_tok.data_ptr(),
