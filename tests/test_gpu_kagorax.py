@@ -373,3 +373,16 @@ def test_random_weights_from_a_configuration(tmp_path):
     b = Engine(d, dtype="bfloat16", page_size=16, num_pages=16, max_requests=2)
     lb = b.step([StepEntry("a", tokens, [0, 50, 89])])
     assert torch.isfinite(la).all() and torch.equal(la, lb)
+
+
+def test_command_line_with_token_ids(tmp_path_factory, capsys):
+    from tinyinfer_b200 import cli
+    d = make_model(tmp_path_factory.getbasetemp(), "A")
+    cfg, w = plain.load_folder(d)
+    prompt = random_tokens(cfg["vocab"], 9, seed=4)
+    rc = cli.main(["-m", d, "--tokens", "-p", " ".join(map(str, prompt)), "-n", "6", "--dtype", "float32",
+                   "--max-seq", "64", "--max-num-seqs", "2", "--page-size", "16"])
+    assert rc == 0
+    out = capsys.readouterr().out
+    line = [ln for ln in out.splitlines() if ln.startswith("[output]")][0]
+    assert [int(x) for x in line.split()[1:]] == plain.greedy(cfg, w, prompt, 6)
