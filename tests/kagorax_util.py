@@ -65,7 +65,18 @@ SMALL_C = {
     ]}
 ROWS_C = [16, 10, 32]
 
-SMALL = {"A": (SMALL_A, ROWS_A), "B": (SMALL_B, ROWS_B), "C": (SMALL_C, ROWS_C)}
+# head size 128: prompt portions take the tcgen05 attention kernel; windows shorter than the prompts,
+# so that tiles of kept first tokens are walked apart from the window's
+SMALL_D = {
+    "architecture": "Kagorax", "vocab": 500, "width": 128, "embedding": {"scale": 9.0}, "norm": {"eps": 1e-6},
+    "layers": [
+        _layer(_mixer(2, 1, 128, 128, 0.09, 260, 150, 3), _moe(4, 2, 32, 32)),
+        _layer(_mixer(4, 2, 128, 128, 0.1, 90, 40, 130), _moe(4, 1, 64)),
+        _layer(_mixer(4, 2, 128, 128, 0.08, 500, 260, 1, kv_from=1), None),
+    ]}
+ROWS_D = [12, 8, 20]
+
+SMALL = {"A": (SMALL_A, ROWS_A), "B": (SMALL_B, ROWS_B), "C": (SMALL_C, ROWS_C), "D": (SMALL_D, ROWS_D)}
 
 
 def random_weights(cfg: dict, table_rows, seed: int) -> dict:

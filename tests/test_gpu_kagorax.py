@@ -19,7 +19,8 @@ from util import FP32_RTOL, assert_close_logits, random_tokens
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
-LENGTHS = {"A": [70, 45, 120, 33, 17, 2, 64], "B": [40, 9, 65, 1], "C": [200, 33, 130, 64, 95, 17]}
+LENGTHS = {"A": [70, 45, 120, 33, 17, 2, 64], "B": [40, 9, 65, 1], "C": [200, 33, 130, 64, 95, 17],
+           "D": [420, 140, 33, 300, 129]}
 
 
 @pytest.fixture(scope="module")
@@ -191,6 +192,8 @@ def test_one_key_carries_the_weight_at_every_edge(ops, where, dtype):
     lets it through, far back among hundreds, at a page's border, just inside and just outside
     the window, and among the kept first tokens."""
     heads, kv, dk, dv, ps = 2, 1, 16, (8 if dtype == torch.float32 else 16), 16
+    if dtype == torch.bfloat16 and where == "long portion":
+        dk = dv = 128                                      # the tcgen05 kernel's head size
     window, keep = 48, 5
     ctx = 400
     n_new = {"decoded": 1, "portion": 3, "long portion": 170}[where]
@@ -200,10 +203,10 @@ def test_one_key_carries_the_weight_at_every_edge(ops, where, dtype):
     for target, seen in cases:
         step, cache, q, keys, values, bt = _attention_case(heads, kv, dk, dv, ps, [ctx], [n_new], dtype, seed=4)
         keys[0].mul_(0.01)
-        keys[0][target] = 3.0
+        keys[0][target] = 3.0 if dk == 16 else 1.0
         values[0][target] = torch.arange(1, dv + 1, dtype=torch.float32)
         _fill_pages(cache, bt, keys, values, kv, dk, dv)
-        q.fill_(3.0)
+        q.fill_(3.0 if dk == 16 else 1.0)
         qd = q.reshape(n_new, heads * dk).to(DEV).to(dtype)
         out = torch.empty((n_new, heads * dv), dtype=dtype, device=DEV)
         dist = torch.zeros((heads, 9), dtype=torch.float32, device=DEV)
@@ -295,7 +298,7 @@ def test_router_and_experts(ops, dtype, sizes):
 
 # ---- the model through the engine ------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_prompts(tmp_path_factory, name, dtype):
     d = make_model(tmp_path_factory.getbasetemp(), name)
     steps = traces.whole(_requests(name))
@@ -306,13 +309,15 @@ def test_whole_prompts(tmp_path_factory, name, dtype):
 @pytest.mark.parametrize("name, family, dtype", [
     ("A", "tail", "float32"), ("A", "portions", "float32"), ("A", "mixed", "float32"), ("A", "mixed", "bfloat16"),
     ("B", "portions", "float32"), ("B", "mixed", "float32"),
-    ("C", "tail", "float32"), ("C", "portions", "bfloat16"), ("C", "mixed", "float32"), ("C", "mixed", "bfloat16")])
+    ("C", "tail", "float32"), ("C", "portions", "bfloat16"), ("C", "mixed", "float32"), ("C", "mixed", "bfloat16"),
+    ("D", "long portions", "bfloat16"), ("D", "long portions", "float32"), ("D", "mixed", "bfloat16")])
 def test_cuttings_agree_with_the_plain_implementation(tmp_path_factory, name, family, dtype):
     """Prefill against token-by-token decoding, portions down to two tokens, and up to four live
     requests of unequal length in a pool so small that pages and slots are used again."""
     d = make_model(tmp_path_factory.getbasetemp(), name)
     reqs = _requests(name)
     steps = {"tail": lambda: traces.tail_decoded(reqs, tail=40), "portions": lambda: traces.portions(reqs),
+             "long portions": lambda: traces.portions(reqs, sizes=(150, 2, 131, 70, 128, 3)),
              "mixed": lambda: traces.mixed(reqs, seed=5)}[family]()
     out = _run(d, dtype, steps, traces.max_live_tokens(steps))
     _compare(steps, out, _plain(d, name), dtype, f"{name} {family}")

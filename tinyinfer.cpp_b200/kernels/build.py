@@ -28,7 +28,7 @@ LIBRARIES = {
              "gemm_tcgen05_few.cu", "ffn_decode.cu", "attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu",
              "attn_prefill_tc2.cu"],
     # tensor-core kernels of the attention with a distance bias and of the routed feed-forward
-    "bf16_gated": ["common.cu", "attn_gated_bias_tc.cu", "moe_grouped.cu"],
+    "bf16_gated": ["common.cu", "attn_gated_bias_tc.cu", "attn_bias_prefill_tc.cu", "moe_grouped.cu"],
 }
 
 # libraries that parts bring themselves: name -> (absolute source paths, include folders)

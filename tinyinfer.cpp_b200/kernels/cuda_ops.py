@@ -128,7 +128,8 @@ class CudaOps:
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._bf16 = None
         self._gated = None
-        self.use_tc_biased_attention = True   # tensor-core prompt kernel of the attention with a distance bias
+        self.use_tc_biased_attention = True   # tensor-core kernels of the attention with a distance bias
+        self.use_tcgen05_biased_attention = True   # ... its prompt portions on tcgen05 where the head size is 128
         self.grouped_experts_from = 128       # (token, slot) pairs from which the experts run as grouped products
         self.tcgen05_experts_from = 1024      # ... and from which those products run on tcgen05
         self._counters = None
@@ -271,6 +272,9 @@ class CudaOps:
             b.ti_attn_bias_prefill_supported.argtypes = [_i, _i, _i]
             b.ti_attn_bias_prefill.argtypes = [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f,
                                                _vp, _i, _vp, _i, _vp, _vp, _vp]
+            b.ti_attn_bias_prefill_tc_supported.argtypes = [_i, _i, _i, _i, _i]
+            b.ti_attn_bias_prefill_tc.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f,
+                                                  _vp, _i, _vp, _i, _vp, _vp, _vp]
             b.ti_attn_bias_decode_supported.argtypes = [_i, _i, _i, _i]
             b.ti_attn_bias_decode.argtypes = [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f,
                                               _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp]
@@ -897,7 +901,24 @@ class CudaOps:
                 and self.gated.ti_attn_bias_prefill_supported(dk, dv, cache.page_size)):
             self.bf16
             tiles = lists[f"portion_tiles_{self._tile_rows[0]}"]
-            if tiles.shape[0]:
+            big = lists.get(f"portion_tiles_{self._tile_rows[1]}")
+            if (tiles.shape[0] and self.use_tcgen05_biased_attention and big is not None
+                    and q.data_ptr() % 16 == 0 and out.data_ptr() % 32 == 0
+                    and (gate is None or (gate.stride(0) % 4 == 0 and gate.data_ptr() % 16 == 0))
+                    and tuple(pages.shape[1:]) == (2, num_kv_heads, cache.page_size, dk)
+                    and self.gated.ti_attn_bias_prefill_tc_supported(dk, dv, cache.page_size, num_heads, num_kv_heads)):
+                # head size 128: the tcgen05 kernel, on tiles of its own height
+                self._ok(self.gated.ti_attn_bias_prefill_tc(
+                    q.data_ptr(), q.shape[0], big.data_ptr(), big.shape[0], step.positions.data_ptr(), bt.data_ptr(),
+                    bt.stride(0), pages.data_ptr(), pages.shape[0], cache.page_size, num_heads, num_kv_heads, dk,
+                    int(window or 0), int(keep_first), float(scale), dist_bias.data_ptr(), dist_bias.shape[1],
+                    _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(),
+                    self.status.data_ptr(), self._stream()), self.gated)
+                rows = lists["single_rows"]
+                n_rows = rows.shape[0]
+                if n_rows == 0:
+                    return
+            elif tiles.shape[0]:
                 self._ok(self.gated.ti_attn_bias_prefill(
                     q.data_ptr(), tiles.data_ptr(), tiles.shape[0], step.positions.data_ptr(), bt.data_ptr(),
                     bt.stride(0), pages.data_ptr(), pages.shape[0], cache.page_size, num_heads, num_kv_heads, dk,
