@@ -11,8 +11,11 @@
 //    the last row's own position.  All three roles count the same `num_kt` tiles; only the TMA
 //    warp and the softmax ask which keys tile j holds (`tile_of`);
 //  * key j is masked for row i when j > i, or when i - j >= window and j >= keep_first;
-//  * a score is (q . k) * scale + bias[head][min(i - j, n_dist - 1)]: a thread reads its row's 128
-//    table entries per tile (neighbouring rows read neighbouring entries), before the maximum;
+//  * a score is (q . k) * scale + bias[head][min(i - j, n_dist - 1)].  A thread needs the 128
+//    consecutive entries bias[d0 - 127 .. d0] of its row per tile (d0: the row's distance to the
+//    tile's first key), so the caller brings the table reversed, padded by 128 entries at both ends
+//    (no clamping) and in four copies shifted by 0..3 entries (`bias_rev4[head][copy][pitch]`): one
+//    of the copies has the thread's run 16-byte aligned, and the run is 32 vector loads;
 //  * the normalised output is multiplied by sigmoid(gate) as it is stored.
 // The keys of a tile are not cut into runs over several blocks here (gridDim.z is 1).
 // Every wait on an mbarrier is bounded; on a timeout the block records status 2, frees its tensor
@@ -47,8 +50,8 @@ attn_bias_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                        const int* __restrict__ tiles, const int* __restrict__ positions,
                        const int* __restrict__ block_table, int bt_stride, int num_pages, int page_size,
                        int num_heads, int num_kv_heads, int window, int keep_first, int run, float scale,
-                       const float* __restrict__ dist_bias, int n_dist, const float* gate, int gate_stride,
-                       bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                       const float* __restrict__ bias_rev4, int n_dist, int bias_pitch, const float* gate,
+                       int gate_stride, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                        int* __restrict__ status, int hold_dependents) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -223,7 +226,7 @@ attn_bias_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int pos_row = row < nrows ? pos_first + row : -1;               // -1: sees nothing
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
         float m_ref = -INFINITY, l_run = 0.0f;
-        const float* bias_h = dist_bias + (size_t)h * n_dist;
+        const float* bias_h = bias_rev4 + (size_t)h * 4 * bias_pitch;
         for (int j = 0; j < num_kt && ok; ++j) {
             const int b = j & 1;
             const int key_lo = tile_of(w_lo + j) * BN;
@@ -241,10 +244,20 @@ attn_bias_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (lane == 0) mbar_arrive(&s_empty[b]);
             // scaled score plus the bias of its distance (a row past the tile reads entry 0)
             {
-                const int d0 = pos_row - key_lo;
+                // reversed, padded table R (length n_dist + 256): bias[clamp(d)] = R[n_dist + 127 - d],
+                // so key i of the tile reads R[base + i]; copy c holds R shifted by c entries
+                const int d0 = min(max(pos_row - key_lo, -1), n_dist + 127);
+                const int base = n_dist + 127 - d0;
+                const int cpy = base & 3;
+                const float4* bp = reinterpret_cast<const float4*>(bias_h + (size_t)cpy * bias_pitch + (base - cpy));
 #pragma unroll
-                for (int i = 0; i < BN; ++i)
-                    v[i] = fmaf(v[i], scale, __ldg(bias_h + min(max(d0 - i, 0), n_dist - 1)));
+                for (int q4 = 0; q4 < BN / 4; ++q4) {
+                    const float4 b4 = __ldg(bp + q4);
+                    v[4 * q4] = fmaf(v[4 * q4], scale, b4.x);
+                    v[4 * q4 + 1] = fmaf(v[4 * q4 + 1], scale, b4.y);
+                    v[4 * q4 + 2] = fmaf(v[4 * q4 + 2], scale, b4.z);
+                    v[4 * q4 + 3] = fmaf(v[4 * q4 + 3], scale, b4.w);
+                }
             }
             if (edge) {
 #pragma unroll
@@ -388,14 +401,16 @@ extern "C" int ti_attn_bias_prefill_tc_supported(int dk, int dv, int page_size, 
 
 // q, out: [tokens, num_heads * 128] bfloat16, contiguous.  pages: the cache slot's pool
 // [num_pages, 2, kv_heads, page_size, 128] bfloat16, contiguous.  tiles: int32 [num_tiles, 3] =
-// {request row, first flat token, query rows (<= 128)}.  dist_bias: float32 [num_heads, n_dist];
+// {request row, first flat token, query rows (<= 128)}.  bias_rev4: float32 [num_heads, 4, bias_pitch],
+// copy c of head h holding R[j + c] at j, where R[k] = bias[h][clamp(n_dist + 127 - k, 0, n_dist - 1)]
+// for k < n_dist + 256 (bias_pitch >= n_dist + 256, a multiple of 4; the table 16-byte aligned);
 // gate (may be null): float32, row t at gate + t * gate_stride, [num_heads * 128], 16-byte aligned.
 extern "C" int ti_attn_bias_prefill_tc(const void* q, int num_tokens, const int* tiles, int num_tiles,
                                        const int* positions, const int* block_table, int bt_stride,
                                        const void* pages, int num_pages, int page_size, int num_heads,
                                        int num_kv_heads, int head_dim, int window, int keep_first, float scale,
-                                       const float* dist_bias, int n_dist, const float* gate, int gate_stride,
-                                       void* out, int* status, void* stream) {
+                                       const float* bias_rev4, int n_dist, int bias_pitch, const float* gate,
+                                       int gate_stride, void* out, int* status, void* stream) {
     if (num_tiles == 0) return 0;
     TI_REQUIRE(ti_attn_bias_prefill_tc_supported(head_dim, head_dim, page_size, num_heads, num_kv_heads),
                "attn_bias_prefill_tc: head_dim %d (128), page size %d (multiple of 16) or heads %d/%d "
@@ -403,7 +418,9 @@ extern "C" int ti_attn_bias_prefill_tc(const void* q, int num_tokens, const int*
     TI_REQUIRE((uintptr_t)q % 16 == 0 && (uintptr_t)pages % 16 == 0 && (uintptr_t)out % 32 == 0,
                "attn_bias_prefill_tc: tensors must be 16-byte aligned, the output 32-byte");
     TI_REQUIRE(num_tiles <= 65535, "attn_bias_prefill_tc: %d tiles exceed the grid limit", num_tiles);
-    TI_REQUIRE(dist_bias != nullptr && n_dist >= 1 && keep_first >= 0, "attn_bias_prefill_tc: no bias table");
+    TI_REQUIRE(bias_rev4 != nullptr && n_dist >= 1 && keep_first >= 0 && bias_pitch >= n_dist + 256 &&
+               bias_pitch % 4 == 0 && (uintptr_t)bias_rev4 % 16 == 0,
+               "attn_bias_prefill_tc: the reversed bias table must be 16-byte aligned with a pitch of at least n_dist + 256");
     TI_REQUIRE(gate == nullptr || ((uintptr_t)gate % 16 == 0 && gate_stride % 4 == 0),
                "attn_bias_prefill_tc: gate rows must be 16-byte aligned");
     const long long pool_rows = (long long)num_pages * 2 * num_kv_heads * page_size;
@@ -425,7 +442,7 @@ extern "C" int ti_attn_bias_prefill_tc(const void* q, int num_tokens, const int*
     dim3 grid(num_heads, num_tiles, 1);
     ti_launch_pdl(attn_bias_prefill_tc_kernel, grid, dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, map_q, map_kv,
                   tiles, positions, block_table, bt_stride, num_pages, page_size, num_heads, num_kv_heads,
-                  window, keep_first, run, scale, dist_bias, n_dist, gate, gate_stride, (bf16*)out,
+                  window, keep_first, run, scale, bias_rev4, n_dist, bias_pitch, gate, gate_stride, (bf16*)out,
                   (float*)nullptr, (float*)nullptr, status, 0);
     return ti_check_launch("attn_bias_prefill_tc");
 }

@@ -128,6 +128,7 @@ class CudaOps:
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._bf16 = None
         self._gated = None
+        self._rev4 = {}
         self.use_tc_biased_attention = True   # tensor-core kernels of the attention with a distance bias
         self.use_tcgen05_biased_attention = True   # ... its prompt portions on tcgen05 where the head size is 128
         self.grouped_experts_from = 128       # (token, slot) pairs from which the experts run as grouped products
@@ -274,7 +275,7 @@ class CudaOps:
                                                _vp, _i, _vp, _i, _vp, _vp, _vp]
             b.ti_attn_bias_prefill_tc_supported.argtypes = [_i, _i, _i, _i, _i]
             b.ti_attn_bias_prefill_tc.argtypes = [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f,
-                                                  _vp, _i, _vp, _i, _vp, _vp, _vp]
+                                                  _vp, _i, _i, _vp, _i, _vp, _vp, _vp]
             b.ti_attn_bias_decode_supported.argtypes = [_i, _i, _i, _i]
             b.ti_attn_bias_decode.argtypes = [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f,
                                               _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp]
@@ -844,6 +845,24 @@ class CudaOps:
                                              float(scale), token_ids.shape[0], table.shape[1],
                                              out.data_ptr(), self._stream()))
 
+    def _reversed_bias(self, dist_bias):
+        """The distance table as the tcgen05 prompt kernel reads it, made once per table:
+        ``[heads, 4, pitch]`` float32, copy c of a head holding ``R[j + c]`` at ``j``, where
+        ``R[k] = bias[clamp(n + 127 - k, 0, n - 1)]`` for ``k < n + 256`` (the table reversed, with 128
+        entries of padding at both ends), so that a row's 128 entries of a key tile are one aligned,
+        ascending run in one of the copies."""
+        key = (dist_bias.data_ptr(), tuple(dist_bias.shape))
+        found = self._rev4.get(key)
+        if found is None:
+            heads, n = dist_bias.shape
+            pitch = (n + 256 + 4 + 3) // 4 * 4
+            k = torch.arange(pitch + 3, device=dist_bias.device)
+            r = dist_bias[:, (n + 127 - k).clamp(0, n - 1)]                      # [heads, pitch + 3]
+            found = torch.stack([r[:, c:c + pitch] for c in range(4)], dim=1).contiguous()
+            self._rev4[key] = (found, dist_bias)             # the table stays alive with its copy
+            return found
+        return found[0]
+
     @staticmethod
     def _page_elems(cache, num_kv_heads, dk, dv) -> int:
         return num_kv_heads * cache.page_size * (dk + dv)
@@ -908,11 +927,12 @@ class CudaOps:
                     and tuple(pages.shape[1:]) == (2, num_kv_heads, cache.page_size, dk)
                     and self.gated.ti_attn_bias_prefill_tc_supported(dk, dv, cache.page_size, num_heads, num_kv_heads)):
                 # head size 128: the tcgen05 kernel, on tiles of its own height
+                rev4 = self._reversed_bias(dist_bias)
                 self._ok(self.gated.ti_attn_bias_prefill_tc(
                     q.data_ptr(), q.shape[0], big.data_ptr(), big.shape[0], step.positions.data_ptr(), bt.data_ptr(),
                     bt.stride(0), pages.data_ptr(), pages.shape[0], cache.page_size, num_heads, num_kv_heads, dk,
-                    int(window or 0), int(keep_first), float(scale), dist_bias.data_ptr(), dist_bias.shape[1],
-                    _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(),
+                    int(window or 0), int(keep_first), float(scale), rev4.data_ptr(), dist_bias.shape[1],
+                    rev4.shape[2], _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(),
                     self.status.data_ptr(), self._stream()), self.gated)
                 rows = lists["single_rows"]
                 n_rows = rows.shape[0]
