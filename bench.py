@@ -464,7 +464,9 @@ def timed_ops(engine, names, run, torch):
             a0.record()
             out = fn(*a, **k)
             a1.record()
-            spans[name].append((a0, a1))
+            # a product is told apart by its weight's shape and whether it adds to its output
+            what = (tuple(a[1].shape), bool(k.get("accumulate", a[3] if len(a) > 3 else False))) if name == "linear" else None
+            spans[name].append((a0, a1, what))
             return out
         return inner
 
@@ -478,7 +480,9 @@ def timed_ops(engine, names, run, torch):
     finally:
         for n in names:
             delattr(ops, n)
-    return {n: [a.elapsed_time(b) for a, b in v] for n, v in spans.items()}
+    out = {n: [a.elapsed_time(b) for a, b, _ in v] for n, v in spans.items()}
+    out["_linear_kinds"] = [what for _, _, what in spans.get("linear", [])]
+    return out
 
 
 def design_arm(args) -> int:
@@ -504,7 +508,8 @@ def design_arm(args) -> int:
         ffn_flops = {"kagorax": 2.0 * prompt_len * 3 * w * (top * ff + shared), "qwen3": 2.0 * prompt_len * 3 * w * (top * ff + shared)}
         ffn_bytes = {"kagorax": 2.0 * 3 * w * (min(experts, batch * top) * ff + shared), "qwen3": 2.0 * 3 * w * (top * ff + shared)}
         for arm, cfg, calls in (
-                ("kagorax", kagorax_config(size), {"attention": ["biased_attention"], "ffn": ["router_topk", "routed_experts", "gate_up_swiglu", "scale_rows"]}),
+                ("kagorax", kagorax_config(size), {"attention": ["biased_attention"], "ffn": ["router_topk", "routed_experts"],
+                             "inside": ["gate_up_swiglu", "scale_rows"]}),   # the shared expert runs inside routed_experts
                 ("qwen3", qwen3_like_config(size, max(context, prompt_len) + 64), {"attention": ["paged_attention"], "ffn": ["swiglu_ffn"]})):
             engine = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=args.page_size,
                             num_pages=-(-max(batch * context, prompt_len) // args.page_size) + batch + 2,
@@ -514,23 +519,27 @@ def design_arm(args) -> int:
             a = {"prefill_tok_s": round(prompt_len / pf_ms * 1e3), "prefill_ms": round(pf_ms, 3),
                  "decode_tok_s": round(batch / ms * 1e3, 1), "decode_ms_per_step": round(ms, 4),
                  "decode_launches_per_step": launches // max(1, args.steps), "clocks": clocks}
-            names = calls["attention"] + calls["ffn"] + (["linear"] if arm == "kagorax" else [])
+            names = calls["attention"] + calls["ffn"] + calls.get("inside", []) + (["linear"] if arm == "kagorax" else [])
             engine._step_graphs = None
             engine.ops.fuse_decode_tail = engine.ops.fuse_decode_ffn = False   # the feed-forward as a call of its own
-            spans = timed_ops(engine, names, lambda: engine.step([StepEntry("p", prompt, [prompt_len - 1])]), torch)
-            engine.finish("p")
+            for _ in range(2):        # the first eager step sizes the allocator's pool; the second is read
+                spans = timed_ops(engine, names, lambda: engine.step([StepEntry("p", prompt, [prompt_len - 1])]), torch)
+                engine.finish("p")
             ids = fill_requests(engine, batch, context - 4, torch)
-            dspans = timed_ops(engine, names, lambda: engine.step([StepEntry(r, [1], [0]) for r in ids]), torch)
+            for _ in range(2):
+                dspans = timed_ops(engine, names, lambda: engine.step([StepEntry(r, [1], [0]) for r in ids]), torch)
             for r in ids:
                 engine.finish(r)
 
             def per_layer(sp, which):
                 return sum(sum(sp[n]) for n in calls[which]) / layers
 
-            if arm == "kagorax":          # a layer calls `linear` four times: projections, output, router,
-                lin, dlin = spans["linear"], dspans["linear"]      # and the shared expert's down product
-                extra = sum(lin[i] for i in range(min(len(lin), 4 * layers)) if i % 4 >= 2) / layers
-                dextra = sum(dlin[i] for i in range(min(len(dlin), 4 * layers)) if i % 4 >= 2) / layers
+            if arm == "kagorax":          # of a layer's products the router's belongs to the feed-forward
+                def ffn_products(sp):     # (the shared expert's are timed inside routed_experts)
+                    router_rows = -(-(experts + 1) // 16) * 16
+                    return sum(ms_ for ms_, ((n_, k_), acc) in zip(sp["linear"], sp["_linear_kinds"])
+                               if n_ == router_rows and k_ == w and not acc) / layers
+                extra, dextra = ffn_products(spans), ffn_products(dspans)
             else:
                 extra = dextra = 0.0
             pa, da = per_layer(spans, "attention"), per_layer(dspans, "attention")
@@ -538,8 +547,8 @@ def design_arm(args) -> int:
             a["per_layer_us"] = {"prompt_attention": round(pa * 1e3, 1), "decode_attention": round(da * 1e3, 1),
                                  "prompt_ffn": round(pff * 1e3, 1), "decode_ffn": round(dff * 1e3, 1)}
             a["calls_per_layer_us"] = {
-                "prompt": {n: round(sum(v) / layers * 1e3, 1) for n, v in spans.items()},
-                "decode": {n: round(sum(v) / layers * 1e3, 1) for n, v in dspans.items()}}
+                "prompt": {n: round(sum(v) / layers * 1e3, 1) for n, v in spans.items() if not n.startswith("_")},
+                "decode": {n: round(sum(v) / layers * 1e3, 1) for n, v in dspans.items() if not n.startswith("_")}}
             a["roofline_frac"] = {
                 "prompt_attention": round(attn_flops / (pa * 1e-3) / (pk["bf16_tflops"] * 1e12), 3),
                 "decode_attention": round(attn_bytes / (da * 1e-3) / (pk["hbm_gbs"] * 1e9), 3),

@@ -9,6 +9,8 @@
 //    matrix, interleaved in strips of 8 or one after the other).  The weight stands for a scaling of the
 //    expert's input: (Wgate (w h), Wup (w h)) = (w g, w u).
 //  * moe_down_simple: out[t] += sum over the slots, in order, of Wdown_e y[t][s].
+//  Both take a shared expert along when one is given: its gate/up products as one more pair per
+//  token with weight 1, its down product added to the token's sum times the token's gate.
 //  * scale_rows: y[t] *= f[t].
 //
 // These are the true 32-bit kernels and the general path of the bfloat16 engine; float32
@@ -87,14 +89,23 @@ __global__ void __launch_bounds__(WARPS * 32)
 moe_gate_up_simple_kernel(const TA* __restrict__ h, int h_stride, const TW* __restrict__ w_gate_up,
                           int interleaved, const int* __restrict__ ids,
                           const float* __restrict__ weights, int top, int width, int ff,
-                          TA* __restrict__ y) {
+                          TA* __restrict__ y, int n_pairs, const TW* __restrict__ shared_gate_up,
+                          int shared_interleaved, int shared_ff, TA* __restrict__ y_shared) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ts = blockIdx.x;                        // token * top + slot
+    int ts = blockIdx.x;                              // token * top + slot; behind the pairs: a token's shared expert
     const int f = blockIdx.y * WARPS + warp;
+    const bool shared = ts >= n_pairs;
+    if (shared) {
+        ts -= n_pairs;                                // the token
+        w_gate_up = shared_gate_up;
+        interleaved = shared_interleaved;
+        ff = shared_ff;
+        y = y_shared;
+    }
     if (f >= ff) return;
-    const int e = ids[ts];
-    const float w = weights[ts];
-    const TA* x = h + (size_t)(ts / top) * h_stride;
+    const int e = shared ? 0 : ids[ts];
+    const float w = shared ? 1.0f : weights[ts];
+    const TA* x = h + (size_t)(shared ? ts : ts / top) * h_stride;
     // an expert's 2 ff rows: strips of 8 gate rows and their 8 up rows, or all gate rows and then all up rows
     const size_t gate_row = interleaved ? (size_t)(f >> 3) * 16 + (f & 7) : (size_t)f;
     const size_t up_row = interleaved ? gate_row + 8 : (size_t)ff + f;
@@ -115,7 +126,9 @@ template <typename TA, typename TW>
 __global__ void __launch_bounds__(WARPS * 32)
 moe_down_simple_kernel(const TA* __restrict__ y, const TW* __restrict__ w_down,
                        const int* __restrict__ ids, int top, int width, int ff,
-                       float* __restrict__ out, int out_stride) {
+                       float* __restrict__ out, int out_stride, const TA* __restrict__ y_shared,
+                       const TW* __restrict__ w_shared_down, const float* __restrict__ shared_gate,
+                       int shared_ff) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const int n = blockIdx.y * WARPS + warp;
@@ -128,6 +141,13 @@ moe_down_simple_kernel(const TA* __restrict__ y, const TW* __restrict__ w_down,
         float acc = 0.0f;
         for (int k = lane; k < ff; k += 32) acc = fmaf(to_f32(ys[k]), to_f32(wd[k]), acc);
         total += warp_sum(acc);
+    }
+    if (y_shared != nullptr) {                        // the shared expert's row, times the token's gate
+        const TA* ys = y_shared + (size_t)t * shared_ff;
+        const TW* wd = w_shared_down + (size_t)n * shared_ff;
+        float acc = 0.0f;
+        for (int k = lane; k < shared_ff; k += 32) acc = fmaf(to_f32(ys[k]), to_f32(wd[k]), acc);
+        total += warp_sum(acc) * shared_gate[t];
     }
     if (lane == 0) out[(size_t)t * out_stride + n] += total;
 }
@@ -165,13 +185,18 @@ extern "C" int ti_router_topk(const float* logits, int stride, int num_tokens, i
 extern "C" int ti_moe_gate_up_simple(const void* h, int act_dtype, int h_stride, const void* w_gate_up,
                                      int interleaved, int w_dtype, const int* ids,
                                      const float* weights, int num_tokens, int top, int width, int ff,
-                                     void* y, void* stream) {
+                                     void* y, const void* shared_gate_up, int shared_interleaved,
+                                     int shared_ff, void* y_shared, void* stream) {
     if (num_tokens == 0) return 0;
-    dim3 grid(num_tokens * top, (ff + WARPS - 1) / WARPS);
+    // with a shared expert (same weight dtype): one more "pair" per token behind the routed ones
+    const bool shared = shared_gate_up != nullptr;
+    const int most = shared && shared_ff > ff ? shared_ff : ff;
+    dim3 grid(num_tokens * top + (shared ? num_tokens : 0), (most + WARPS - 1) / WARPS);
     cudaStream_t s = (cudaStream_t)stream;
 #define CALL(TA, TW)                                                                         \
     moe_gate_up_simple_kernel<TA, TW><<<grid, WARPS * 32, 0, s>>>(                            \
-        (const TA*)h, h_stride, (const TW*)w_gate_up, interleaved, ids, weights, top, width, ff, (TA*)y)
+        (const TA*)h, h_stride, (const TW*)w_gate_up, interleaved, ids, weights, top, width, ff, (TA*)y, \
+        num_tokens * top, (const TW*)shared_gate_up, shared_interleaved, shared_ff, (TA*)y_shared)
     TI_DISPATCH_AW(act_dtype, w_dtype, CALL)
 #undef CALL
     return ti_check_launch("moe_gate_up_simple");
@@ -179,13 +204,16 @@ extern "C" int ti_moe_gate_up_simple(const void* h, int act_dtype, int h_stride,
 
 extern "C" int ti_moe_down_simple(const void* y, int act_dtype, const void* w_down, int w_dtype,
                                   const int* ids, int num_tokens, int top, int width, int ff,
-                                  float* out, int out_stride, void* stream) {
+                                  float* out, int out_stride, const void* y_shared,
+                                  const void* w_shared_down, const float* shared_gate, int shared_ff,
+                                  void* stream) {
     if (num_tokens == 0) return 0;
     dim3 grid(num_tokens, (width + WARPS - 1) / WARPS);
     cudaStream_t s = (cudaStream_t)stream;
 #define CALL(TA, TW)                                                                         \
     moe_down_simple_kernel<TA, TW><<<grid, WARPS * 32, 0, s>>>(                               \
-        (const TA*)y, (const TW*)w_down, ids, top, width, ff, out, out_stride)
+        (const TA*)y, (const TW*)w_down, ids, top, width, ff, out, out_stride, (const TA*)y_shared, \
+        (const TW*)w_shared_down, shared_gate, shared_ff)
     TI_DISPATCH_AW(act_dtype, w_dtype, CALL)
 #undef CALL
     return ti_check_launch("moe_down_simple");

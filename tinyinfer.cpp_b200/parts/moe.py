@@ -80,12 +80,10 @@ class RoutedExperts(Part):
         if self.shared_size is not None:
             shared_gate = torch.empty((t,), dtype=torch.float32, device=h.device)
         ops.router_topk(logits, self.experts, self.top, ids, weights, shared_gate)
-        ops.routed_experts(h, self.w_experts, ids, weights, residual)
+        shared = None
         if self.shared_size is not None:
-            y = torch.empty((t, self.shared_size), dtype=h.dtype, device=h.device)
-            ops.gate_up_swiglu(h, self.w_shared_gate_up, y)
-            ops.scale_rows(y, shared_gate)
-            ops.linear(y, self.w_shared_down, residual, accumulate=True)
+            shared = (self.w_shared_gate_up, self.w_shared_down, shared_gate)
+        ops.routed_experts(h, self.w_experts, ids, weights, residual, shared)
 
 
 register_part("ffn", "routed_experts", RoutedExperts)
