@@ -49,6 +49,23 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// The pairs of every expert counted in shared memory by one block; a thread has SORT_UNROLL loads
+// of ids in flight at once (with one at a time the block waited a round trip per 1,024 pairs).
+constexpr int SORT_UNROLL = 8;
+__device__ __forceinline__ void count_pairs(const int* __restrict__ ids, int n_pairs, int experts, int* counts) {
+    for (int base = threadIdx.x; base < n_pairs; base += blockDim.x * SORT_UNROLL) {
+        int e[SORT_UNROLL];
+#pragma unroll
+        for (int u = 0; u < SORT_UNROLL; ++u) {
+            const int i = base + u * blockDim.x;
+            e[u] = i < n_pairs ? __ldg(ids + i) : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < SORT_UNROLL; ++u)
+            if (e[u] >= 0 && e[u] < experts) atomicAdd(&counts[e[u]], 1);
+    }
+}
+
 // meta: [0] = number of tiles.  tiles: [max_tiles][3] = {expert, first sorted row, rows}.
 __global__ void __launch_bounds__(1024)
 moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ sorted_slot,
@@ -58,10 +75,7 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __re
     int* offsets = sh + experts;
     for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-        const int e = ids[i];
-        if (e >= 0 && e < experts) atomicAdd(&counts[e], 1);
-    }
+    count_pairs(ids, n_pairs, experts, counts);
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0, nt = 0;
@@ -81,9 +95,17 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __re
     __syncthreads();
     // the order of an expert's pairs among themselves is left to the atomics: every row of a
     // product is computed from its own operands alone, so no result depends on it
-    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-        const int e = ids[i];
-        if (e >= 0 && e < experts) sorted_slot[offsets[e] + atomicAdd(&counts[e], 1)] = i;
+    for (int base = threadIdx.x; base < n_pairs; base += blockDim.x * SORT_UNROLL) {
+        int e[SORT_UNROLL];
+#pragma unroll
+        for (int u = 0; u < SORT_UNROLL; ++u) {
+            const int i = base + u * blockDim.x;
+            e[u] = i < n_pairs ? __ldg(ids + i) : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < SORT_UNROLL; ++u)
+            if (e[u] >= 0 && e[u] < experts)
+                sorted_slot[offsets[e[u]] + atomicAdd(&counts[e[u]], 1)] = base + u * blockDim.x;
     }
 }
 
@@ -240,10 +262,7 @@ moe_sort_padded_kernel(const int* __restrict__ ids, int n_pairs, int experts, in
     for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
     for (int r = threadIdx.x; r < max_rows; r += blockDim.x) row_pair[r] = -1;
     __syncthreads();
-    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-        const int e = ids[i];
-        if (e >= 0 && e < experts) atomicAdd(&counts[e], 1);
-    }
+    count_pairs(ids, n_pairs, experts, counts);
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0, nt = 0;
@@ -257,12 +276,21 @@ moe_sort_padded_kernel(const int* __restrict__ ids, int n_pairs, int experts, in
         tiles_m[0] = nt;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-        const int e = ids[i];
-        if (e < 0 || e >= experts) continue;
-        const int pos = offsets[e] + atomicAdd(&counts[e], 1);
-        row_pair[pos] = i;
-        pos_of_pair[i] = pos;
+    for (int base = threadIdx.x; base < n_pairs; base += blockDim.x * SORT_UNROLL) {
+        int e[SORT_UNROLL];
+#pragma unroll
+        for (int u = 0; u < SORT_UNROLL; ++u) {
+            const int i = base + u * blockDim.x;
+            e[u] = i < n_pairs ? __ldg(ids + i) : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < SORT_UNROLL; ++u) {
+            if (e[u] < 0 || e[u] >= experts) continue;
+            const int i = base + u * blockDim.x;
+            const int pos = offsets[e[u]] + atomicAdd(&counts[e[u]], 1);
+            row_pair[pos] = i;
+            pos_of_pair[i] = pos;
+        }
     }
 }
 
@@ -292,12 +320,17 @@ __global__ void moe_gather_scaled_kernel(const bf16* __restrict__ h, int h_strid
 
 __global__ void moe_combine_rows_kernel(const float* __restrict__ rows, const int* __restrict__ pos_of_pair, int top,
                                         int width, int num_tokens, float* __restrict__ residual, int res_stride) {
+    const int quads = width >> 2;                      // width is a multiple of 8 on this path
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (size_t)num_tokens * width) return;
-    const int t = (int)(i / width), c = (int)(i % width);
-    float total = 0.0f;
-    for (int s = 0; s < top; ++s) total += rows[(size_t)pos_of_pair[t * top + s] * width + c];
-    residual[(size_t)t * res_stride + c] += total;
+    if (i >= (size_t)num_tokens * quads) return;
+    const int t = (int)(i / quads), c = (int)(i % quads) * 4;
+    float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int s = 0; s < top; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(rows + (size_t)pos_of_pair[t * top + s] * width + c);
+        total.x += v.x; total.y += v.y; total.z += v.z; total.w += v.w;
+    }
+    float* dst = residual + (size_t)t * res_stride + c;
+    dst[0] += total.x; dst[1] += total.y; dst[2] += total.z; dst[3] += total.w;
 }
 
 }  // namespace
@@ -323,7 +356,8 @@ extern "C" int ti_moe_gather_scaled(const void* h, int h_stride, const int* row_
 
 extern "C" int ti_moe_combine_rows(const float* rows, const int* pos_of_pair, int top, int width, int num_tokens,
                                    float* residual, int res_stride, void* stream) {
-    const size_t total = (size_t)num_tokens * width;
+    TI_REQUIRE(width % 4 == 0 && ((uintptr_t)rows) % 16 == 0, "moe_combine_rows: rows of four-float groups, 16-byte aligned");
+    const size_t total = (size_t)num_tokens * (width / 4);
     if (total == 0) return 0;
     moe_combine_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
         rows, pos_of_pair, top, width, num_tokens, residual, res_stride);
