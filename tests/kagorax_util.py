@@ -76,7 +76,19 @@ SMALL_D = {
     ]}
 ROWS_D = [12, 8, 20]
 
-SMALL = {"A": (SMALL_A, ROWS_A), "B": (SMALL_B, ROWS_B), "C": (SMALL_C, ROWS_C), "D": (SMALL_D, ROWS_D)}
+# sizes that no tensor-core kernel takes (a width that is no multiple of 32, head sizes that are no
+# multiples of 16, an odd table): every call must find its general kernel, in both precisions
+SMALL_E = {
+    "architecture": "Kagorax", "vocab": 301, "width": 72, "embedding": {"scale": 5.0}, "norm": {"eps": 3e-6},
+    "layers": [
+        _layer(_mixer(3, 1, 40, 24, 0.16, 77, 50, 2), _moe(5, 2, 24, 40)),
+        _layer(_mixer(6, 3, 8, 8, 0.35, 30, 19, 9), _moe(3, 3, 56)),
+        _layer(_mixer(6, 3, 8, 8, 0.3, 45, 64, 0, kv_from=1), _moe(7, 1, 8, 8)),
+    ]}
+ROWS_E = [9, 6, 14]
+
+SMALL = {"A": (SMALL_A, ROWS_A), "B": (SMALL_B, ROWS_B), "C": (SMALL_C, ROWS_C), "D": (SMALL_D, ROWS_D),
+         "E": (SMALL_E, ROWS_E)}
 
 
 def random_weights(cfg: dict, table_rows, seed: int) -> dict:

@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 LENGTHS = {"A": [70, 45, 120, 33, 17, 2, 64], "B": [40, 9, 65, 1], "C": [200, 33, 130, 64, 95, 17],
-           "D": [420, 140, 33, 300, 129]}
+           "D": [420, 140, 33, 300, 129], "E": [150, 70, 9, 260, 66]}
 
 
 @pytest.fixture(scope="module")
@@ -298,7 +298,7 @@ def test_router_and_experts(ops, dtype, sizes):
 
 # ---- the model through the engine ------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole_prompts(tmp_path_factory, name, dtype):
     d = make_model(tmp_path_factory.getbasetemp(), name)
     steps = traces.whole(_requests(name))
@@ -310,7 +310,8 @@ def test_whole_prompts(tmp_path_factory, name, dtype):
     ("A", "tail", "float32"), ("A", "portions", "float32"), ("A", "mixed", "float32"), ("A", "mixed", "bfloat16"),
     ("B", "portions", "float32"), ("B", "mixed", "float32"),
     ("C", "tail", "float32"), ("C", "portions", "bfloat16"), ("C", "mixed", "float32"), ("C", "mixed", "bfloat16"),
-    ("D", "long portions", "bfloat16"), ("D", "long portions", "float32"), ("D", "mixed", "bfloat16")])
+    ("D", "long portions", "bfloat16"), ("D", "long portions", "float32"), ("D", "mixed", "bfloat16"),
+    ("E", "long portions", "bfloat16"), ("E", "mixed", "float32"), ("E", "mixed", "bfloat16"), ("E", "tail", "bfloat16")])
 def test_cuttings_agree_with_the_plain_implementation(tmp_path_factory, name, family, dtype):
     """Prefill against token-by-token decoding, portions down to two tokens, and up to four live
     requests of unequal length in a pool so small that pages and slots are used again."""
