@@ -25,6 +25,43 @@ constexpr int MAX_TOP = 32;
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 
+// A lane's share of x . a and x . b over `n` elements.  bfloat16 operands whose rows are 16-byte
+// aligned go eight elements a load (a warp then asks for 512 contiguous bytes of a weight row at
+// once, instead of 64); everything else one element at a time.
+template <typename TA, typename TW>
+__device__ __forceinline__ void lane_dots(const TA* __restrict__ x, const TW* __restrict__ a, const TW* __restrict__ b,
+                                          int n, int lane, float& ra, float& rb) {
+    ra = rb = 0.0f;
+    if constexpr (sizeof(TA) == 2 && sizeof(TW) == 2) {
+        const bool vec = n % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)a % 16 == 0) &&
+                         (b == nullptr || (uintptr_t)b % 16 == 0);
+        if (vec) {
+            for (int k = lane * 8; k < n; k += 256) {
+                const uint4 xv = *reinterpret_cast<const uint4*>(x + k);
+                const uint4 av = *reinterpret_cast<const uint4*>(a + k);
+                const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+                const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&av);
+                uint4 bv = make_uint4(0u, 0u, 0u, 0u);
+                if (b != nullptr) bv = *reinterpret_cast<const uint4*>(b + k);
+                const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 xf = __bfloat1622float2(xp[i]), af = __bfloat1622float2(ap[i]);
+                    const float2 bf = __bfloat1622float2(bp[i]);
+                    ra = fmaf(xf.x, af.x, ra); ra = fmaf(xf.y, af.y, ra);
+                    rb = fmaf(xf.x, bf.x, rb); rb = fmaf(xf.y, bf.y, rb);
+                }
+            }
+            return;
+        }
+    }
+    for (int k = lane; k < n; k += 32) {
+        const float xv = to_f32(x[k]);
+        ra = fmaf(xv, to_f32(a[k]), ra);
+        if (b != nullptr) rb = fmaf(xv, to_f32(b[k]), rb);
+    }
+}
+
 __global__ void __launch_bounds__(WARPS * 32)
 router_topk_kernel(const float* logits, int stride, int num_tokens, int experts, int top,
                    int shared_col, int* __restrict__ ids, float* __restrict__ weights,
@@ -111,12 +148,8 @@ moe_gate_up_simple_kernel(const TA* __restrict__ h, int h_stride, const TW* __re
     const size_t up_row = interleaved ? gate_row + 8 : (size_t)ff + f;
     const TW* wg = w_gate_up + ((size_t)e * 2 * ff + gate_row) * width;
     const TW* wu = w_gate_up + ((size_t)e * 2 * ff + up_row) * width;
-    float g = 0.0f, u = 0.0f;
-    for (int k = lane; k < width; k += 32) {
-        const float xv = to_f32(x[k]);
-        g = fmaf(xv, to_f32(wg[k]), g);
-        u = fmaf(xv, to_f32(wu[k]), u);
-    }
+    float g, u;
+    lane_dots(x, wg, wu, width, lane, g, u);
     g = warp_sum(g) * w;
     u = warp_sum(u) * w;
     if (lane == 0) y[(size_t)ts * ff + f] = from_f32<TA>(g * sigmoidf_(g) * u);
@@ -138,15 +171,15 @@ moe_down_simple_kernel(const TA* __restrict__ y, const TW* __restrict__ w_down,
         const int e = ids[(size_t)t * top + s];
         const TA* ys = y + ((size_t)t * top + s) * ff;
         const TW* wd = w_down + ((size_t)e * width + n) * ff;
-        float acc = 0.0f;
-        for (int k = lane; k < ff; k += 32) acc = fmaf(to_f32(ys[k]), to_f32(wd[k]), acc);
+        float acc, unused;
+        lane_dots(ys, wd, (const TW*)nullptr, ff, lane, acc, unused);
         total += warp_sum(acc);
     }
     if (y_shared != nullptr) {                        // the shared expert's row, times the token's gate
         const TA* ys = y_shared + (size_t)t * shared_ff;
         const TW* wd = w_shared_down + (size_t)n * shared_ff;
-        float acc = 0.0f;
-        for (int k = lane; k < shared_ff; k += 32) acc = fmaf(to_f32(ys[k]), to_f32(wd[k]), acc);
+        float acc, unused;
+        lane_dots(ys, wd, (const TW*)nullptr, shared_ff, lane, acc, unused);
         total += warp_sum(acc) * shared_gate[t];
     }
     if (lane == 0) out[(size_t)t * out_stride + n] += total;
