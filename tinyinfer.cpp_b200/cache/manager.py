@@ -8,7 +8,9 @@ values), so that a page id addresses the same tokens in every layer of the group
 Groups with different needs have pools of their own.  A group with a window gives
 a page back as soon as every position on it lies behind the window of the
 request's next token, except the pages that hold the request's first ``keep_first``
-tokens, which stay readable; all pages go back when the request ends.  Values may have a
+tokens, which stay readable; a group whose mixer reads only the current chunk of
+positions gives back the pages that lie wholly in earlier chunks; all pages go back
+when the request ends.  Values may have a
 head size of their own: a page is then a flat run of its keys followed by its values.  Nothing is cleared
 on reuse: kernels read only positions below the request's length.
 
@@ -67,9 +69,12 @@ class _PagedGroup:
     def first_needed_block(self, length: int) -> int:
         """Index of the first block behind the kept first tokens that the token at position
         ``length`` may still read."""
-        if self.spec.window is None:
-            return 0
-        return max(0, length - self.spec.window + 1) // self.page_size
+        first = 0
+        if self.spec.window is not None:
+            first = max(0, length - self.spec.window + 1)
+        if self.spec.chunk is not None:            # the chunk that the next token falls into
+            first = max(first, length // self.spec.chunk * self.spec.chunk)
+        return first // self.page_size
 
     @property
     def kept_blocks(self) -> int:
@@ -236,7 +241,7 @@ class CacheManager:
         freed = 0
         length = self._lengths[req]
         for g in self.groups:
-            if g.spec.window is None:
+            if g.spec.window is None and g.spec.chunk is None:
                 continue
             table = g.tables[req]
             for b in range(g.kept_blocks, min(g.first_needed_block(length), len(table))):

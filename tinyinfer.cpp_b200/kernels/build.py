@@ -29,6 +29,8 @@ LIBRARIES = {
              "attn_prefill_tc2.cu"],
     # tensor-core kernels of the attention with a distance bias and of the routed feed-forward
     "bf16_gated": ["common.cu", "attn_gated_bias_tc.cu", "attn_bias_prefill_tc.cu", "moe_grouped.cu"],
+    # attention with optional parts (chunks, caps, sinks, gates, shared rows) and the recurrent mixer
+    "mixers": ["common.cu", "attn_options.cu", "wkv.cu"],
 }
 
 # libraries that parts bring themselves: name -> (absolute source paths, include folders)

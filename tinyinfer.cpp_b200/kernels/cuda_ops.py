@@ -36,6 +36,7 @@ from typing import Optional
 import torch
 
 from .build import load_library
+from .mixer_ops import MixerOps
 
 _CODE = {torch.float32: 0, torch.bfloat16: 1}
 _vp = ctypes.c_void_p
@@ -109,7 +110,7 @@ def choose_prompt_attention(n_tiles: int, num_heads: int, num_sms: int, *, reach
     return two, runs
 
 
-class CudaOps:
+class CudaOps(MixerOps):
     name = "cuda"
 
     def __init__(self, device):
@@ -1161,7 +1162,7 @@ def _flush_first(fn):
     return wrapper
 
 
-for _name, _fn in list(vars(CudaOps).items()):
+for _name, _fn in list(vars(MixerOps).items()) + list(vars(CudaOps).items()):
     if (isinstance(_fn, type(_flush_first)) and not _name.startswith("_")
             and _name not in ("flush", "linear", "rmsnorm", "swiglu_ffn")):
         setattr(CudaOps, _name, _flush_first(_fn))

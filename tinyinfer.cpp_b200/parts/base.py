@@ -32,6 +32,7 @@ from ..config.plan import PartSpec
 
 MATRIX = "matrix"        # random mode: N(0, 0.02), stored in bfloat16
 NORM_WEIGHT = "norm"     # random mode: 1 + N(0, 0.02), stored in float32
+NORM_ZERO = "norm0"      # random mode: N(0, 0.02), stored in float32 (a factor stored minus one, a vector)
 
 
 @dataclass(frozen=True)
@@ -43,12 +44,17 @@ class WeightSpec:
 @dataclass(frozen=True)
 class PagedKVSpec:
     """Keys and values of every past token (or of the last ``window`` tokens, and of the
-    request's first ``keep_first`` tokens whatever the window) in pages."""
+    request's first ``keep_first`` tokens whatever the window; or of the tokens of the current
+    ``chunk`` of positions) in pages."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: all keys are kept
-    v_head_dim: Optional[int] = None # None: values have the keys' head size
+    v_head_dim: Optional[int] = None # None: values have the keys' head size; 0: a page holds one row
+                                     # per token and kv head only (a mixer that makes keys and
+                                     # values from the same cached row)
     keep_first: int = 0              # a request's first tokens stay readable behind the window
+    chunk: Optional[int] = None      # positions are cut into chunks of this size, counted from 0,
+                                     # and a token reads only keys of its own chunk
 
 
 @dataclass(frozen=True)

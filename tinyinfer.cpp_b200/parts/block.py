@@ -2,7 +2,7 @@
 
 ``prenorm`` (reference: src/inference.cu:35-66): ``x += mixer(norm1(x))`` then
 ``x += ffn(norm2(x))``; both sums happen in the float32 residual stream, inside the
-mixer's and the feed-forward's last product.
+mixer's and the feed-forward's last product.  A layer without a feed-forward stops after the mixer.
 
 ``parallel``: ``h = norm(x)``, then ``x += mixer(h)`` and ``x += ffn(h)``.
 """
@@ -14,13 +14,16 @@ from .base import Part, register_part
 class PreNormBlock(Part):
     category = "block"
 
-    def __init__(self, mixer, ffn, mixer_norm, ffn_norm):
+    def __init__(self, mixer, mixer_norm, ffn=None, ffn_norm=None):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
         self.mixer, self.ffn = mixer, ffn
         self.mixer_norm, self.ffn_norm = mixer_norm, ffn_norm
 
     def forward(self, ops, x, step, cache):
         self.mixer.forward(ops, self.mixer_norm.forward(ops, x, step.act_dtype), x, step, cache)
-        self.ffn.forward(ops, self.ffn_norm.forward(ops, x, step.act_dtype), x, step)
+        if self.ffn is not None:
+            self.ffn.forward(ops, self.ffn_norm.forward(ops, x, step.act_dtype), x, step)
 
 
 class ParallelBlock(Part):

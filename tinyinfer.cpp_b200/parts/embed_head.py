@@ -2,7 +2,7 @@
 
 Embedding: ``x[t] = float32(E[token[t]])`` without scaling (reference:
 src/inference.cu:14-24); ``scaled_sinusoid``: the row times a constant plus a sine/cosine
-wave of the token's position.  Head: ``logits = h E_out^T`` in float32, where ``E_out``
+wave of the token's position; ``normed``: the row under an RMSNorm with a weight of its own.  Head: ``logits = h E_out^T`` in float32, where ``E_out``
 is the embedding table when the head is tied (reference: always tied,
 src/inference.cu:70-71) or a table of its own.
 """
@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import MATRIX, Part, WeightSpec, register_part
+from .base import MATRIX, NORM_WEIGHT, NORM_ZERO, Part, WeightSpec, as_float32, register_part
 
 
 class Embedding(Part):
@@ -60,21 +60,48 @@ class SinusoidEmbedding(Embedding):
         ops.embed_sinusoid(self.table, token_ids, positions, self.freq, self.scale, out)
 
 
+class NormedEmbedding(Embedding):
+    """``x[t] = norm(E[token[t]])``: RMSNorm of the table's row (float32) with a weight of the
+    model's width; ``one_plus``: the stored weight is the factor minus one."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, eps: float, tensor: str = "weight",
+                 norm_tensor: str = "norm.weight", one_plus: bool = False):
+        super().__init__(vocab_size, hidden_size)
+        self.eps, self.tensor, self.norm_tensor = float(eps), str(tensor), str(norm_tensor)
+        self.one_plus = bool(one_plus)
+        self.norm_weight = None
+
+    def weight_specs(self):
+        return {self.tensor: WeightSpec((self.vocab_size, self.hidden_size), MATRIX),
+                self.norm_tensor: WeightSpec((self.hidden_size,), NORM_ZERO if self.one_plus else NORM_WEIGHT)}
+
+    def load_weights(self, tensors, ops):
+        self.table = ops.pack_linear(tensors[self.tensor])
+        w = as_float32(tensors[self.norm_tensor]).contiguous()
+        self.norm_weight = 1.0 + w if self.one_plus else w
+
+    def forward(self, ops, token_ids, out):
+        rows = torch.empty_like(out)
+        ops.embed(self.table, token_ids, rows)
+        ops.rmsnorm(rows, self.norm_weight, self.eps, out)
+
+
 class LMHead(Part):
     category = "head"
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied: bool):
+    def __init__(self, vocab_size: int, hidden_size: int, tied: bool, tensor: str = "weight"):
         self.vocab_size, self.hidden_size, self.tied = int(vocab_size), int(hidden_size), bool(tied)
+        self.tensor = str(tensor)
         self.table = None
 
     def weight_specs(self):
         if self.tied:
             return {}
-        return {"weight": WeightSpec((self.vocab_size, self.hidden_size), MATRIX)}
+        return {self.tensor: WeightSpec((self.vocab_size, self.hidden_size), MATRIX)}
 
     def load_weights(self, tensors, ops):
         if not self.tied:
-            self.table = ops.pack_linear(tensors["weight"])
+            self.table = ops.pack_linear(tensors[self.tensor])
 
     def tie(self, embedding: Embedding):
         self.table = embedding.shared_weights()["weight"]
@@ -87,4 +114,5 @@ class LMHead(Part):
 
 register_part("embedding", "embedding", Embedding)
 register_part("embedding", "scaled_sinusoid", SinusoidEmbedding)
+register_part("embedding", "normed", NormedEmbedding)
 register_part("head", "lm_head", LMHead)

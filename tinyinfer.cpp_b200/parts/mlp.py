@@ -3,8 +3,12 @@
 ``silu(g) = g / (1 + exp(-g))`` in float32 (reference: src/cuda/ffn.cu:13-15;
 gate and up as one product over stacked rows, src/inference.cu:59-65).  How the
 gate and up rows are stacked is the kernel set's choice (``ops.pack_gate_up``).
+
+``xielu_mlp``: an ungated feed-forward with the xIELU activation (below).
 """
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -39,3 +43,39 @@ class SwiGLU(Part):
 
 
 register_part("ffn", "swiglu", SwiGLU)
+
+
+def _softplus(z: float) -> float:
+    return math.log1p(math.exp(-abs(z))) + max(z, 0.0)
+
+
+class XieluMlp(Part):
+    """``residual += Wdown act(Wup h)`` with ``act`` = xIELU and its two stored numbers ``p, q``:
+    ``softplus(p) z^2 + z/2`` for ``z > 0``, ``(1/2 + softplus(q)) (exp(z) - 1 - z) + z/2`` elsewhere.
+    The two factors are made once, in double precision, when the weights are loaded."""
+    category = "ffn"
+
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.w_up = self.w_down = None
+        self.ap = self.aq = 0.0
+
+    def weight_specs(self):
+        h, i = self.hidden_size, self.intermediate_size
+        return {"up": WeightSpec((i, h), MATRIX), "down": WeightSpec((h, i), MATRIX),
+                "act": WeightSpec((2,), MATRIX)}
+
+    def load_weights(self, tensors, ops):
+        self.w_up, self.w_down = ops.pack_linear(tensors["up"]), ops.pack_linear(tensors["down"])
+        p, q = (float(v) for v in tensors["act"].to(torch.float64).cpu())
+        self.ap, self.aq = _softplus(p), 0.5 + _softplus(q)
+
+    def forward(self, ops, h, residual, step):
+        z = torch.empty((h.shape[0], self.intermediate_size), dtype=torch.float32, device=h.device)
+        ops.linear(h, self.w_up, z)
+        y = torch.empty(z.shape, dtype=h.dtype, device=h.device)
+        ops.xielu_rows(z, self.ap, self.aq, y)
+        ops.linear(y, self.w_down, residual, accumulate=True, may_defer=True)
+
+
+register_part("ffn", "xielu_mlp", XieluMlp)

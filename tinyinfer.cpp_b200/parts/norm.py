@@ -1,4 +1,5 @@
-"""RMSNorm: ``x * rsqrt(mean(x^2) + eps) * w``, eps inside the root, weight applied directly.
+"""RMSNorm: ``x * rsqrt(mean(x^2) + eps) * w``, eps inside the root, weight applied directly;
+with ``one_plus`` the stored weight lies around zero and the factor is ``1 + w``.
 
 Formula as in the reference's ``rms_norm_kernel`` (src/cuda/rms_norm.cu:15-25).
 All arithmetic is float32; the result is rounded once to the output dtype.
@@ -13,10 +14,11 @@ from .base import NORM_WEIGHT, Part, WeightSpec, as_float32, register_part
 class RMSNorm(Part):
     category = "norm"
 
-    def __init__(self, size: int, eps: float, tensor: str = "weight"):
+    def __init__(self, size: int, eps: float, tensor: str = "weight", one_plus: bool = False):
         self.size = int(size)
         self.eps = float(eps)
         self.tensor = str(tensor)            # the weight's name behind the part's prefix (may be empty)
+        self.one_plus = bool(one_plus)       # the stored weight is the factor minus one
         self.weight: torch.Tensor | None = None
 
     def weight_specs(self):
@@ -24,6 +26,8 @@ class RMSNorm(Part):
 
     def load_weights(self, tensors, ops):
         self.weight = as_float32(tensors[self.tensor]).contiguous()
+        if self.one_plus:
+            self.weight = 1.0 + self.weight          # float32; the kernels multiply by it as it is
 
     def forward(self, ops, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         out = torch.empty((x.shape[0], self.size), dtype=out_dtype, device=x.device)

@@ -14,6 +14,10 @@ Kinds built in:
            ``(x0 cos a - x1 sin a, x0 sin a + x1 cos a)``; elements from ``rotary_dim`` on are
            left as they are.  With ``rotary_dim = head_dim`` this is the reference's rotation
            (src/cuda/attention.cu:64-74, src/cuda/rope.cu:19-28).
+``interleaved``  neighbouring pairs over the first ``rotary_dim`` elements of a head: elements
+           ``2k`` and ``2k + 1`` form pair ``k`` with the same frequencies and the same turn as
+           above.  The kernels that take it say so (``ops.qk_rownorm_rope_store``,
+           ``ops.latent_prepare``); the per-head norm kernel of ``neox`` does not.
 ``none``   no rotation (``rotary_dim = 0``).
 
 ``inv_freq`` is computed once on the host in double precision and rounded to float32; the
@@ -71,6 +75,13 @@ class RopeNeox(Part):
         return Rotation("neox", self.rotary_dim, _TABLES[key])
 
 
+class RopeInterleaved(RopeNeox):
+    """The same frequencies and turn as ``RopeNeox`` on neighbouring pairs ``(2k, 2k + 1)``."""
+
+    def rotation(self, device) -> Rotation:
+        return Rotation("interleaved", self.rotary_dim, super().rotation(device).inv_freq)
+
+
 class NoPosition(Part):
     """Heads are normed and stored without a rotation."""
     category = "position"
@@ -83,4 +94,5 @@ class NoPosition(Part):
 
 
 register_part("position", "rope_neox", RopeNeox)
+register_part("position", "rope_interleaved", RopeInterleaved)
 register_part("position", "none", NoPosition)

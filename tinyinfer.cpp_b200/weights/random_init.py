@@ -1,6 +1,7 @@
 """Random weights from a configuration and a seed.
 
-Matrices and embedding tables are N(0, 0.02); every norm weight is 1 + N(0, 0.02).
+Matrices and embedding tables are N(0, 0.02); every norm weight is 1 + N(0, 0.02) (N(0, 0.02)
+where a factor is stored minus one).
 The generator is counter-based: element ``i`` of a tensor is a function of (seed, tensor name, i)
 alone, made of integer arithmetic and two float32 operations, so a tensor's values do not depend
 on which other tensors exist, in which order they are drawn or in how many pieces, and the CPU
@@ -22,7 +23,7 @@ from typing import Any, Mapping
 import torch
 
 from ..config.registry import architecture_of
-from ..parts.base import MATRIX, NORM_WEIGHT, WeightSpec
+from ..parts.base import MATRIX, NORM_WEIGHT, NORM_ZERO, WeightSpec
 from ..parts.model import CausalLM
 from .safetensors_io import write_safetensors
 
@@ -67,7 +68,7 @@ def standard_normal(key: int, start: int, count: int, device="cpu") -> torch.Ten
 
 def random_tensor(seed: int, name: str, spec: WeightSpec, device="cpu",
                   dtype: torch.dtype | None = None) -> torch.Tensor:
-    if spec.init == NORM_WEIGHT:
+    if spec.init in (NORM_WEIGHT, NORM_ZERO):
         default = torch.float32
     elif spec.init == MATRIX:
         default = torch.bfloat16
