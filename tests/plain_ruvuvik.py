@@ -26,7 +26,7 @@ def norm_plain(x, weight, eps):
 
 
 def norm_one_plus(x, weight, eps):
-    """The model's norm: its weight is stored around zero."""
+    """The model's norm: the stored weight is the factor minus one."""
     return unit_rms(x, eps) * (1.0 + weight)
 
 
@@ -64,6 +64,27 @@ def softmax_rows(scores: torch.Tensor, extra: float | None = None) -> torch.Tens
     return e / den
 
 
+def attend(q, keys, values, positions, scale, chunk=None, cap=None, head_scale=None, sink=None):
+    """Causal softmax attention of queries ``q`` [T, H, dk] at ``positions`` over ``keys`` [S, G, dk]
+    and ``values`` [S, G, dv] at positions 0 .. S-1.  A query at i sees j <= i of its own chunk
+    (``j // chunk == i // chunk``); the score is (q . k) * scale [* head_scale[h]], then
+    cap * tanh(score / cap); ``sink`` [H] adds one logit without a value to the denominator."""
+    t, nh, _ = q.shape
+    g = keys.shape[1]
+    out = torch.zeros((t, nh, values.shape[2]), dtype=q.dtype)
+    for r, i in enumerate(positions):
+        lo = 0 if chunk is None else (i // chunk) * chunk
+        for a in range(nh):
+            kv = a // (nh // g)
+            s = (keys[lo:i + 1, kv] @ q[r, a]) * scale
+            if head_scale is not None:
+                s = s * head_scale[a]
+            if cap is not None:
+                s = cap * torch.tanh(s / cap)
+            out[r, a] = softmax_rows(s, None if sink is None else float(sink[a])) @ values[lo:i + 1, kv]
+    return out
+
+
 # ---- mixers --------------------------------------------------------------------------------
 def chunked_attention(h, w, p, m, eps, first_position=0, past=None):
     """Grouped-query attention inside chunks of ``mask.size`` positions.  ``past``: (keys, values)
@@ -79,15 +100,7 @@ def chunked_attention(h, w, p, m, eps, first_position=0, past=None):
     if past is not None:
         k, v = torch.cat([past[0], k]), torch.cat([past[1], v])
     gate = torch.sigmoid(h @ w[p + "g"].T)                        # [T, H]
-    size, cap = m["mask"]["size"], m["softcap"]
-    out = torch.zeros((t, nh, dv), dtype=h.dtype)
-    for r, i in enumerate(pos):
-        lo = (i // size) * size
-        for a in range(nh):
-            kv = a // (nh // g)
-            s = (k[lo:i + 1, kv] @ q[r, a]) * m["scale"] * w[p + "temp"][a]
-            s = cap * torch.tanh(s / cap)
-            out[r, a] = softmax_rows(s) @ v[lo:i + 1, kv] * gate[r, a]
+    out = attend(q, k, v, pos, m["scale"], m["mask"]["size"], m["softcap"], w[p + "temp"]) * gate[:, :, None]
     return out.reshape(t, nh * dv) @ w[p + "o"].T, (k, v)
 
 
@@ -105,13 +118,10 @@ def latent_attention(h, w, p, m, eps, first_position=0, past=None):
     k_rot = rotate_pairs(down[:, rank:].reshape(t, 1, dr), pos, m["rot"]["dims"], m["rot"]["base"])[:, 0]
     if past is not None:
         c, k_rot = torch.cat([past[0], c]), torch.cat([past[1], k_rot])
-    keys = (c @ w[p + "uk"].T).view(-1, nh, dk)
+    # every head's key: its own plain part followed by the shared rotated part
+    keys = torch.cat([(c @ w[p + "uk"].T).view(-1, nh, dk), k_rot[:, None, :].expand(-1, nh, -1)], dim=2)
     values = (c @ w[p + "uv"].T).view(-1, nh, dv)
-    out = torch.zeros((t, nh, dv), dtype=h.dtype)
-    for r, i in enumerate(pos):
-        for a in range(nh):
-            s = (keys[:i + 1, a] @ q_plain[r, a] + k_rot[:i + 1] @ q_rot[r, a]) * m["scale"]
-            out[r, a] = softmax_rows(s, float(w[p + "sink"][a])) @ values[:i + 1, a]
+    out = attend(torch.cat([q_plain, q_rot], dim=2), keys, values, pos, m["scale"], sink=w[p + "sink"])
     return out.reshape(t, nh * dv) @ w[p + "o"].T, (c, k_rot)
 
 
@@ -177,3 +187,35 @@ def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, carry=None, k
     logits = norm_one_plus(x, w["final.norm"], eps) @ w["head"].T
     carry = (first + len(tokens), caches)
     return (logits, carry, torch.stack(after)) if keep_layers else (logits, carry)
+
+
+def load_folder(model_dir: str):
+    """``(config dictionary, {tensor name: tensor})`` of a model folder, read with the standard
+    library and torch alone."""
+    import json
+    import os
+    import struct
+    with open(os.path.join(model_dir, "config.json")) as fh:
+        cfg = json.load(fh)
+    kinds = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16, "I32": torch.int32}
+    with open(os.path.join(model_dir, "model.safetensors"), "rb") as fh:
+        (n,) = struct.unpack("<Q", fh.read(8))
+        header = json.loads(fh.read(n))
+        data = fh.read()
+    weights = {}
+    for name, ent in header.items():
+        if name == "__metadata__":
+            continue
+        lo, hi = ent["data_offsets"]
+        weights[name] = torch.frombuffer(bytearray(data[lo:hi]), dtype=kinds[ent["dtype"]]).view(ent["shape"]).clone()
+    return cfg, weights
+
+
+def greedy(cfg, weights, prompt, count: int):
+    """``count`` tokens chosen by the largest logit (ties: the lowest id), from ``prompt`` on."""
+    logits, carry = forward(cfg, weights, prompt)
+    out = []
+    for _ in range(count):
+        out.append(int(torch.argmax(logits[-1])))
+        logits, carry = forward(cfg, weights, [out[-1]], carry=carry)
+    return out
