@@ -563,6 +563,120 @@ def design_arm(args) -> int:
     return 0
 
 
+# ---- the Ruvuvik decoder beside the Qwen3 decoder at equal sizes --------------------------------
+# (width, heads, kv heads, head size, chunk, latent rank, rotated part, recurrent head size, ff, blocks of
+# [attention, latent attention, recurrent] layers)
+RUVUVIK_SIZES = {
+    "w1024": (1024, 16, 4, 64, 1024, 256, 32, 64, 2816, 2),
+    "w2048": (2048, 16, 4, 128, 2048, 512, 64, 64, 5632, 2),
+    "w4096": (4096, 32, 8, 128, 4096, 512, 64, 64, 11008, 1),
+}
+
+
+def ruvuvik_config(size):
+    w, h, g, d, chunk, rank, dr, rd, ff, blocks = size
+    mlp = {"kind": "dense", "ff": ff}
+    layers = [
+        {"type": "attention", "mlp": mlp,
+         "mixer": {"heads": h, "kv_heads": g, "dim": d, "vdim": d, "mask": {"size": chunk},
+                   "rot": {"dims": d, "base": 500000.0}, "scale": d ** -0.5, "softcap": 30.0}},
+        {"type": "latent_attention", "mlp": mlp,
+         "mixer": {"heads": h, "dim": d, "rot_dim": dr, "vdim": d, "kv_rank": rank,
+                   "rot": {"dims": dr, "base": 1000000.0}, "scale": (d + dr) ** -0.5}},
+        {"type": "wkv", "mlp": mlp, "mixer": {"heads": w // rd, "dim": rd, "decay_rank": 64}}]
+    return {"architecture": "Ruvuvik", "vocab": DESIGN_VOCAB, "width": w, "norm": {"eps": 1e-5},
+            "layers": layers * blocks}
+
+
+def qwen3_beside_ruvuvik(size, context):
+    w, h, g, d, chunk, rank, dr, rd, ff, blocks = size
+    return dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=3 * blocks, hidden_size=w,
+                num_attention_heads=h, num_key_value_heads=g, head_dim=d, intermediate_size=ff * 2 // 3 // 64 * 64,
+                vocab_size=DESIGN_VOCAB, rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                max_position_embeddings=context)
+
+
+def ruvuvik_arm(args) -> int:
+    """Prefill and decode throughput of the Ruvuvik decoder at sizes of real layers, beside the
+    Qwen3 decoder with as many layers of the same width, heads and head size (its feed-forward has
+    three matrices of two thirds the inner width, so the feed-forwards move as many bytes), and the
+    time the device spends in every kind of kernel call per layer, with the fraction of the
+    roofline for the calls that have one."""
+    import torch
+    from tinyinfer_b200 import Engine, StepEntry
+    pk, pk_kind = peaks()
+    prompt_len, batch, context = args.prefill_tokens, args.batch, args.context
+    warmup = max(args.warmup, 3)
+    out = {"design": "ruvuvik", "beside": "qwen3 at equal sizes", "peaks": pk_kind, "prefill_tokens": prompt_len,
+           "decode_batch": batch, "decode_context": context, "dtype": "bf16", "data": "synthetic", "sizes": {}}
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, DESIGN_VOCAB, (prompt_len,), generator=g).tolist()
+    for key, size in RUVUVIK_SIZES.items():
+        if args.design_size and key != args.design_size:
+            continue
+        w, h, kvh, d, chunk, rank, dr, rd, ff, blocks = size
+        res = {}
+        calls = {"ruvuvik": ["attention_options", "qk_rownorm_rope_store", "latent_prepare", "head_project",
+                             "token_shift_mix", "wkv_recurrence", "tanh_rows", "xielu_rows", "linear", "rmsnorm"],
+                 "qwen3": ["paged_attention", "qkv_rope_store", "swiglu_ffn", "linear", "rmsnorm"]}
+        for arm, cfg in (("ruvuvik", ruvuvik_config(size)),
+                         ("qwen3", qwen3_beside_ruvuvik(size, max(context, prompt_len) + 64))):
+            engine = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=args.page_size,
+                            num_pages=-(-max(batch * context, prompt_len) // args.page_size) + batch + 2,
+                            max_requests=batch + 1, step_graphs=True)
+            pf_ms = measure_prefill(engine, prompt_len, max(1, min(args.steps, 6)), torch)
+            ms, clocks, launches = measure_decode(engine, batch, context, args.steps, warmup, torch)
+            a = {"prefill_tok_s": round(prompt_len / pf_ms * 1e3), "prefill_ms": round(pf_ms, 3),
+                 "decode_tok_s": round(batch / ms * 1e3, 1), "decode_ms_per_step": round(ms, 4),
+                 "decode_launches_per_step": launches // max(1, args.steps), "clocks": clocks}
+            engine._step_graphs = None
+            engine.ops.fuse_decode_tail = engine.ops.fuse_decode_ffn = False   # every call of its own
+            names = calls[arm]
+            for _ in range(2):        # the first eager step sizes the allocator's pool; the second is read
+                spans = timed_ops(engine, names, lambda: engine.step([StepEntry("p", prompt, [prompt_len - 1])]), torch)
+                engine.finish("p")
+            ids = fill_requests(engine, batch, context - 4, torch)
+            for _ in range(2):
+                dspans = timed_ops(engine, names, lambda: engine.step([StepEntry(r, [1], [0]) for r in ids]), torch)
+            for r in ids:
+                engine.finish(r)
+            n_layers = 3 * blocks
+            a["calls_us"] = {
+                "prompt": {n: [round(x * 1e3, 1) for x in v[:12]] for n, v in spans.items() if not n.startswith("_") and n != "linear"},
+                "decode": {n: [round(x * 1e3, 1) for x in v[:12]] for n, v in dspans.items() if not n.startswith("_") and n != "linear"}}
+            a["per_layer_us"] = {
+                "prompt": {n: round(sum(v) / n_layers * 1e3, 1) for n, v in spans.items() if not n.startswith("_")},
+                "decode": {n: round(sum(v) / n_layers * 1e3, 1) for n, v in dspans.items() if not n.startswith("_")}}
+            # rooflines of the attention calls: useful flops of a prompt, cache bytes of a decode step
+            if arm == "ruvuvik":
+                seen_chunk = sum(i % chunk + 1 for i in range(prompt_len))
+                seen_all = prompt_len * (prompt_len + 1) / 2
+                att = spans["attention_options"]
+                datt = dspans["attention_options"]
+                row = rank + dr
+                a["roofline_frac"] = {
+                    "prompt_chunked_attention": round(4.0 * h * d * seen_chunk / (att[0] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                    # the latent form multiplies rows of rank + rotated part and sums rows of rank
+                    "prompt_latent_attention": round(2.0 * h * (row + rank) * seen_all / (att[1] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                    "decode_chunked_attention": round(batch * kvh * ((context - 1) % chunk + 1) * 2 * d * 2.0 / (datt[0] * 1e-3) / (pk["hbm_gbs"] * 1e9), 4),
+                    "decode_latent_attention": round(batch * context * row * 2.0 / (datt[1] * 1e-3) / (pk["hbm_gbs"] * 1e9), 4),
+                    # the recurrence reads r, k, v, g and the decay's argument (float32) and writes a row
+                    "prompt_recurrence_bytes": round(prompt_len * w * (5 * 4 + 2.0) / (spans["wkv_recurrence"][0] * 1e-3) / (pk["hbm_gbs"] * 1e9), 4),
+                    "decode_recurrence_state_bytes": round(batch * (w // rd) * rd * rd * 8.0 / (dspans["wkv_recurrence"][0] * 1e-3) / (pk["hbm_gbs"] * 1e9), 4)}
+            else:
+                att, datt = spans["paged_attention"], dspans["paged_attention"]
+                a["roofline_frac"] = {
+                    "prompt_attention": round(4.0 * h * d * prompt_len * (prompt_len + 1) / 2 / (att[0] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                    "decode_attention": round(batch * kvh * context * 2 * d * 2.0 / (datt[0] * 1e-3) / (pk["hbm_gbs"] * 1e9), 4)}
+            res[arm] = a
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][key] = {"width": w, "heads": h, "kv_heads": kvh, "head_dim": d, "chunk": chunk, "kv_rank": rank,
+                             "rot_dim": dr, "recurrent_head": rd, "ff": ff, "layers": 3 * blocks, **res}
+    print(json.dumps(out))
+    return 0
+
+
 def reference_binary():
     """The reference's command-line program, built with its own CMakeLists if it is not there yet.
     Returns (path, None) or (None, why not)."""
@@ -714,9 +828,10 @@ def main() -> int:
                     help="with --only mixed: the number of decoding requests beside the 512-token portion")
     ap.add_argument("--attention-in-turn", action="store_true",
                     help="with --only mixed: flash-decoding behind the prompt attention kernel, not beside it")
-    ap.add_argument("--design", choices=["kagorax"], default=None,
+    ap.add_argument("--design", choices=["kagorax", "ruvuvik"], default=None,
                     help="set this decoder beside the Qwen3 decoder at equal sizes instead of the default run")
-    ap.add_argument("--design-size", choices=list(DESIGN_SIZES), default=None, help="one of the sizes only")
+    ap.add_argument("--design-size", choices=sorted(set(DESIGN_SIZES) | set(RUVUVIK_SIZES)), default=None,
+                    help="one of the sizes only")
     ap.add_argument("--only", choices=["decode", "prefill", "chains", "mixed"], default=None,
                     help="run one part only and print a short line (for profiling small cases)")
     args = ap.parse_args()
@@ -727,6 +842,8 @@ def main() -> int:
         print(f"bench.py measures one GPU; this engine does no work on several (asked for {args.gpus})")
         return 2
     warmup = max(args.warmup, 3)
+    if args.design == "ruvuvik":
+        return ruvuvik_arm(args)
     if args.design:
         return design_arm(args)
 

@@ -102,8 +102,12 @@ def _paged(ctx_lens, q_lens, page_size, row_elems, dtype, seed=0):
         positions += list(range(c - ql, c))
         req_of_tok += [i] * ql
     ti = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    step = SimpleNamespace(positions=ti(positions), req_of_tok=ti(req_of_tok), scratch={}, lists={},
-                           max_position=max(ctx_lens), max_ctx_len=max(ctx_lens))
+    # the tile lists that the tensor-core kernel walks, for every number of heads per kv head
+    from tinyinfer_b200.kernels.step_lists import row_tiles
+    lists = {f"row_tiles_{n}": ti(row_tiles(list(q_lens), [c - n_ for c, n_ in zip(ctx_lens, q_lens)], n).tolist()).view(-1, 3)
+             for n in (1, 2, 4, 8, 16, 32, 64)}
+    step = SimpleNamespace(positions=ti(positions), req_of_tok=ti(req_of_tok), scratch={}, lists=lists,
+                           max_position=max(ctx_lens), max_ctx_len=max(ctx_lens), max_q_len=max(q_lens))
     pages = torch.zeros((num_pages, page_size * row_elems), dtype=dtype, device=DEV)
     cache = SimpleNamespace(pages=pages, block_table=bt.to(DEV), page_size=page_size, writes=True)
     return step, cache, bt, positions, req_of_tok
@@ -152,12 +156,19 @@ OPTIONS = [dict(chunk=7, cap=3.0, head_scale=True), dict(chunk=64, cap=None, hea
            dict(chunk=None, cap=None)]
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, "bfloat16 on CUDA cores"])
 @pytest.mark.parametrize("opt", OPTIONS)
-@pytest.mark.parametrize("geom", [(4, 2, 12, 8, 8), (1, 1, 16, 16, 16), (6, 1, 40, 24, 16), (8, 2, 64, 64, 64), (2, 2, 160, 130, 16)])
-def test_attention_with_options(ops, geom, opt, dtype):
+@pytest.mark.parametrize("geom", [(4, 2, 12, 8, 8), (1, 1, 16, 16, 16), (6, 1, 40, 24, 16), (8, 2, 64, 64, 64), (2, 2, 160, 130, 16),
+                                  (12, 4, 96, 48, 32), (16, 2, 128, 128, 16), (5, 1, 32, 80, 16), (70, 1, 48, 16, 16)])
+@pytest.mark.parametrize("shape", ["mixed", "decoding"])
+def test_attention_with_options(ops, geom, opt, dtype, shape, monkeypatch):
     heads, kv, dk, dv, ps = geom
-    ctx, ql = [70, 9, 129, 40, 1, 300], [70, 1, 30, 2, 1, 1]
+    if dtype == "bfloat16 on CUDA cores":
+        if dk % 16 or dv % 16 or ps % 16:
+            pytest.skip("these sizes run on the CUDA cores anyway")
+        dtype = torch.bfloat16
+        monkeypatch.setattr(ops, "use_tc_attention_options", False)
+    ctx, ql = ([70, 9, 129, 40, 1, 300], [70, 1, 30, 2, 1, 1]) if shape == "mixed" else ([700, 9, 129, 1], [1, 1, 1, 1])
     step, cache, bt, positions, req = _paged(ctx, ql, ps, kv * (dk + dv), dtype, seed=dk)
     g = torch.Generator().manual_seed(dv)
     keys = [torch.randn((c, kv, dk), generator=g) for c in ctx]
@@ -259,7 +270,7 @@ def test_head_project(ops, sizes, dtype):
 
 
 # ---- mixers alone ----------------------------------------------------------------------------
-def _run_mixer(ops, part, inputs, cuts, dtype, page_size=8):
+def _run_mixer(ops, part, inputs, cuts, dtype, page_size=16):
     """Run a mixer part over requests whose rows ``inputs[r]`` [T_r, width] arrive cut as ``cuts``
     (a list of steps, each a list of (request, count)); returns its output rows per request."""
     from tinyinfer_b200.cache import CacheManager
@@ -274,7 +285,8 @@ def _run_mixer(ops, part, inputs, cuts, dtype, page_size=8):
         entries = [StepEntry(r, [0] * n, []) for r, n in step_cuts]
         starts = cm.reserve_step([(r, n) for r, n in step_cuts])
         tables = [[cm.block_table(g, r) for r, _ in step_cuts] for g in range(len(cm.groups))]
-        batch = build_step_batch(entries, starts, tables, [cm.state_slot(r) for r, _ in step_cuts], dtype, DEV)
+        batch = build_step_batch(entries, starts, tables, [cm.state_slot(r) for r, _ in step_cuts], dtype, DEV,
+                                 lists=ops.step_lists(dtype))
         h = torch.cat([inputs[r][at[r]:at[r] + n] for r, n in step_cuts]).to(dtype).to(DEV)
         residual = torch.zeros((h.shape[0], width), dtype=torch.float32, device=DEV)
         part.forward(ops, h, residual, batch, cm.view(0, True, batch.block_tables, batch.state_slots))

@@ -31,6 +31,7 @@ LIBRARIES = {
     "bf16_gated": ["common.cu", "attn_gated_bias_tc.cu", "attn_bias_prefill_tc.cu", "moe_grouped.cu"],
     # attention with optional parts (chunks, caps, sinks, gates, shared rows) and the recurrent mixer
     "mixers": ["common.cu", "attn_options.cu", "wkv.cu"],
+    "bf16_mixers": ["common.cu", "attn_options_tc.cu"],
 }
 
 # libraries that parts bring themselves: name -> (absolute source paths, include folders)

@@ -298,9 +298,11 @@ class CudaOps(MixerOps):
         prompt-attention kernel's own height.  The 32-bit kernels need none."""
         if act_dtype != torch.bfloat16:
             return []
-        from .step_lists import attention_lists
+        from .step_lists import attention_lists, row_tile_lists
         self.bf16
-        return attention_lists(self._tile_rows)
+        # ... and, where a mixer has announced attention with options, every entry cut into tiles
+        # of as many tokens as that kernel's blocks take
+        return attention_lists(self._tile_rows) + row_tile_lists(self._row_tile_tokens)
 
     def stream(self) -> int:
         """The CUDA stream (as an integer handle) on which the engine's kernels are launched; a

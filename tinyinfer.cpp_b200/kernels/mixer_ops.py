@@ -34,6 +34,40 @@ def _ptr(t):
 
 class MixerOps:
     _mixers = None
+    _mixers_tc = None
+    use_tc_attention_options = True        # tensor-core kernel of the attention with options (bfloat16)
+
+    @property
+    def _row_tile_tokens(self) -> set:
+        found = self.__dict__.get("_row_tile_set")
+        if found is None:
+            found = self.__dict__["_row_tile_set"] = set()
+        return found
+
+    def want_row_tiles(self, num_heads: int, num_kv_heads: int) -> None:
+        """A mixer says, when it gets its weights, that it will call ``attention_options`` with these
+        head counts: every step then brings the tile list that the tensor-core kernel walks
+        (``step_lists``); without it the calls run on the CUDA-core kernel."""
+        self._row_tile_tokens.add(64 // self._group_rows(num_heads, num_kv_heads))
+
+    @staticmethod
+    def _group_rows(num_heads: int, num_kv_heads: int) -> int:
+        gp = 1
+        while gp < num_heads // num_kv_heads and gp < 64:
+            gp *= 2
+        return gp
+
+    @property
+    def mixers_tc(self):
+        if self._mixers_tc is None:
+            b = load_library("bf16_mixers")
+            b.ti_last_error.restype = ctypes.c_char_p
+            b.ti_attn_options_tc_supported.argtypes = [_i, _i, _i, _i]
+            b.ti_attn_options_tc_group_rows.argtypes = [_i, _i]
+            b.ti_attn_options_tc.argtypes = [_vp, _vp, _i, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i,
+                                             _f, _f, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]
+            self._mixers_tc = b
+        return self._mixers_tc
 
     @property
     def mixers(self):
@@ -166,6 +200,36 @@ class MixerOps:
         self._must(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == t
                                     and gate.shape[1] == (num_heads if gate_per_head else num_heads * dv)),
                    "attention_options: the gate must be float32 [T, heads] or [T, heads * dv]")
+        gp = self._group_rows(num_heads, num_kv_heads)
+        tiles = getattr(step, "lists", {}).get(f"row_tiles_{64 // gp}")
+        if (self.use_tc_attention_options and tiles is not None and q.dtype == torch.bfloat16
+                and pages.dtype == torch.bfloat16 and q.data_ptr() % 16 == 0 and out.data_ptr() % 4 == 0
+                and pages.data_ptr() % 16 == 0
+                and self.mixers_tc.ti_attn_options_tc_supported(dk, dv, cache.page_size, int(bool(shared_rows)))
+                and self.mixers_tc.ti_attn_options_tc_group_rows(num_heads, num_kv_heads) == gp):
+            # a step of single tokens has few blocks: the keys of a row in runs, a block each; the
+            # count depends on the step's shape and the model's bounds alone
+            nsplit, part_o, part_ml = 1, None, None
+            slices = dv // (128 if dv % 128 == 0 else 64 if dv % 64 == 0 else 32 if dv % 32 == 0 else 16)
+            blocks = tiles.shape[0] * num_kv_heads * -(-(num_heads // num_kv_heads) // gp) * slices
+            if getattr(step, "max_q_len", 0) == 1 and blocks < 2 * self.num_sms:
+                most = step.max_position or step.max_ctx_len
+                for bound in (window, chunk):
+                    if bound:
+                        most = min(most, int(bound))
+                nsplit = max(1, min(2 * self.num_sms // blocks, -(-most // 64) // 2, 64))
+            if nsplit > 1:
+                part_o = torch.empty((t, num_heads, nsplit, dv), dtype=torch.float32, device=q.device)
+                part_ml = torch.empty((t, num_heads, nsplit, 2), dtype=torch.float32, device=q.device)
+                self.launches += 1
+            self._ok(self.mixers_tc.ti_attn_options_tc(
+                q.data_ptr(), tiles.data_ptr(), tiles.shape[0], t, step.positions.data_ptr(), bt.data_ptr(),
+                bt.stride(0), pages.data_ptr(), pages.shape[0], cache.page_size, num_heads, num_kv_heads, dk, dv,
+                int(bool(shared_rows)), int(window or 0), int(chunk or 0), float(scale), float(softcap or 0.0),
+                _ptr(head_scale), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                int(bool(gate_per_head)), nsplit, _ptr(part_o), _ptr(part_ml), out.data_ptr(),
+                self.status.data_ptr(), self._stream()), self.mixers_tc)
+            return
         self._mx(self.mixers.ti_attention_options(
             q.data_ptr(), _CODE[q.dtype], None, step.positions.data_ptr(), step.req_of_tok.data_ptr(),
             bt.data_ptr(), bt.stride(0), pages.data_ptr(), _CODE[pages.dtype], pages.shape[0], cache.page_size,

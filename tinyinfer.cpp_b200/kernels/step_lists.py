@@ -39,6 +39,23 @@ def portion_tiles(q_lens: Sequence[int], starts: Sequence[int], rows: int) -> np
     return np.asarray([x[1:] for x in found], dtype=np.int64).reshape(-1, 3)
 
 
+def row_tiles(q_lens: Sequence[int], starts: Sequence[int], tokens: int) -> np.ndarray:
+    """``[n, 3]`` {request row, first flat token, tokens} of every entry of the step, single tokens
+    included, cut into tiles of ``tokens`` consecutive tokens, in batch order."""
+    q = np.asarray(q_lens, dtype=np.int64)
+    cu = np.concatenate([[0], np.cumsum(q)])
+    per = -(-q // tokens)                                   # tiles of each entry
+    req = np.repeat(np.arange(len(q)), per)
+    first = np.arange(per.sum()) - np.repeat(np.cumsum(per) - per, per)      # index of the tile in its entry
+    lo = first * tokens
+    return np.stack([req, cu[req] + lo, np.minimum(tokens, q[req] - lo)], axis=1).astype(np.int64).reshape(-1, 3)
+
+
+def row_tile_lists(token_counts: Sequence[int]):
+    from ..engine.batch import StepList
+    return [StepList(f"row_tiles_{n}", partial(row_tiles, tokens=n)) for n in sorted(set(token_counts))]
+
+
 def attention_lists(tile_heights: Sequence[int]):
     from ..engine.batch import StepList
     out = [StepList("single_rows", single_rows), StepList("portion_rows", portion_rows)]

@@ -70,6 +70,8 @@ class ChunkedAttention(Part):
         self.q_norm = as_float32(tensors["q.norm"]).contiguous()
         self.k_norm = as_float32(tensors["k.norm"]).contiguous()
         self.temp = as_float32(tensors["temp"]).contiguous() if self.head_temperature else None
+        if hasattr(ops, "want_row_tiles"):
+            ops.want_row_tiles(self.num_heads, self.num_kv_heads)
 
     def cache_spec(self):
         return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window,

@@ -63,6 +63,8 @@ class LatentAttention(Part):
         self.w_uk = tensors["uk"].view(nh, self.head_dim, self.rank).contiguous()
         # [heads, rank, dv]: a head's weighted sum of latents times this is its value
         self.w_uv = tensors["uv"].view(nh, self.v_head_dim, self.rank).transpose(1, 2).contiguous()
+        if hasattr(ops, "want_row_tiles"):
+            ops.want_row_tiles(nh, 1)
 
     def cache_spec(self):
         return PagedKVSpec(1, self.row, self.window, 0)
