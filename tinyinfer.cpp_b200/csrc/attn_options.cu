@@ -143,19 +143,22 @@ latent_prepare_kernel(const float* proj, int stride, const float* __restrict__ l
         dst[rank + e] = from_f32<TC>(turned(lat + rank, e, pos, inv_freq, 1.0f));
 }
 
-// out[t, h, n] = sum_k in[t, h, k] * w[h, k, n]; a block has TT tokens of one head and 128 columns
-constexpr int HP_TOKENS = 8;
+// out[t, h, n] = sum_k in[t, h, k] * w[h, k, n]; a block has 16 tokens of one head and 128 columns;
+// the tokens' inputs lie in shared memory with the tokens of one k side by side, so that a thread
+// reads them four at a time, the same address for the whole warp
+constexpr int HP_TOKENS = 16;
 template <typename TI, typename TW, typename TO>
 __global__ void __launch_bounds__(128)
 head_project_kernel(const TI* in, int in_stride_t, int in_stride_h, const TW* __restrict__ w, int n_in,
                     int n_out, TO* out, int out_stride_t, int out_stride_h, int num_tokens) {
-    extern __shared__ float xs[];                    // [HP_TOKENS][n_in]
+    extern __shared__ __align__(16) float xs[];      // [n_in][HP_TOKENS]
     const int t0 = blockIdx.x * HP_TOKENS, h = blockIdx.y;
     const int n = blockIdx.z * 128 + threadIdx.x;
     const int nt = min(HP_TOKENS, num_tokens - t0);
     for (int e = threadIdx.x; e < HP_TOKENS * n_in; e += 128) {
         const int tt = e / n_in, k = e % n_in;
-        xs[e] = tt < nt ? to_f32(in[(size_t)(t0 + tt) * in_stride_t + (size_t)h * in_stride_h + k]) : 0.0f;
+        xs[k * HP_TOKENS + tt] =
+            tt < nt ? to_f32(in[(size_t)(t0 + tt) * in_stride_t + (size_t)h * in_stride_h + k]) : 0.0f;
     }
     __syncthreads();
     if (n >= n_out) return;
@@ -163,13 +166,22 @@ head_project_kernel(const TI* in, int in_stride_t, int in_stride_h, const TW* __
 #pragma unroll
     for (int i = 0; i < HP_TOKENS; ++i) acc[i] = 0.0f;
     const TW* wh = w + (size_t)h * n_in * n_out + n;
+#pragma unroll 4
     for (int k = 0; k < n_in; ++k) {
         const float wv = to_f32(wh[(size_t)k * n_out]);
+        const float4* x4 = reinterpret_cast<const float4*>(xs + k * HP_TOKENS);
 #pragma unroll
-        for (int i = 0; i < HP_TOKENS; ++i) acc[i] = fmaf(xs[i * n_in + k], wv, acc[i]);
+        for (int i = 0; i < HP_TOKENS / 4; ++i) {
+            const float4 x = x4[i];
+            acc[4 * i] = fmaf(x.x, wv, acc[4 * i]);
+            acc[4 * i + 1] = fmaf(x.y, wv, acc[4 * i + 1]);
+            acc[4 * i + 2] = fmaf(x.z, wv, acc[4 * i + 2]);
+            acc[4 * i + 3] = fmaf(x.w, wv, acc[4 * i + 3]);
+        }
     }
-    for (int i = 0; i < nt; ++i)
-        out[(size_t)(t0 + i) * out_stride_t + (size_t)h * out_stride_h + n] = from_f32<TO>(acc[i]);
+#pragma unroll
+    for (int i = 0; i < HP_TOKENS; ++i)
+        if (i < nt) out[(size_t)(t0 + i) * out_stride_t + (size_t)h * out_stride_h + n] = from_f32<TO>(acc[i]);
 }
 
 struct AttnOptions {

@@ -17,7 +17,8 @@
 // Few rows (decoding) cut the keys of a tile into runs, a block each, whose unnormalised
 // results a second launch adds (attn_options_merge).
 //
-// Precision.  Scores, cap, softmax weights and sums are float32.  The weighted sum of the values
+// Precision.  Scores, cap (with the hardware's float32 exponential and reciprocal, relative error
+// about 2^-22), softmax weights and sums are float32.  The weighted sum of the values
 // also takes the weights in full float32: a weight is split into three bfloat16 parts (8 + 8 + 8
 // bits of its significand), each multiplies the bfloat16 values on the tensor cores, and the
 // three products are added in the float32 accumulator.
@@ -56,17 +57,27 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ unsigned pack_bf16(bf16 lo, bf16 hi) {
-    __nv_bfloat162 v;
-    v.x = lo; v.y = hi;
-    return *reinterpret_cast<unsigned*>(&v);
+// Two floats as three pairs of bfloat16 whose sums are the floats: the upper 16 bits of a float
+// are a bfloat16 (truncated), what is left is exact in float32 and is cut the same way again;
+// after three cuts nothing of the 24-bit significand is left.
+__device__ __forceinline__ void split3_pair(float x, float y, unsigned& hi, unsigned& mid, unsigned& lo) {
+    const unsigned xb = __float_as_uint(x), yb = __float_as_uint(y);
+    hi = __byte_perm(xb, yb, 0x7632);
+    const float x1 = x - __uint_as_float(xb & 0xffff0000u), y1 = y - __uint_as_float(yb & 0xffff0000u);
+    const unsigned x1b = __float_as_uint(x1), y1b = __float_as_uint(y1);
+    mid = __byte_perm(x1b, y1b, 0x7632);
+    const float x2 = x1 - __uint_as_float(x1b & 0xffff0000u), y2 = y1 - __uint_as_float(y1b & 0xffff0000u);
+    lo = __byte_perm(__float_as_uint(x2), __float_as_uint(y2), 0x7632);
 }
-// a float as three bfloat16 parts whose sum is the float
-__device__ __forceinline__ void split3(float p, bf16& a, bf16& b, bf16& c) {
-    a = __float2bfloat16_rn(p);
-    const float r1 = p - __bfloat162float(a);
-    b = __float2bfloat16_rn(r1);
-    c = __float2bfloat16_rn(r1 - __bfloat162float(b));
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 struct TcOptions {
@@ -137,6 +148,7 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
         row_lo[r] = row_h[r] >= 0 ? first_visible(row_pos[r], opt) : 0;
         row_scale[r] = opt.scale * ((opt.head_scale && row_h[r] >= 0) ? opt.head_scale[row_h[r]] : 1.0f);
     }
+    const float cap_arg = opt.softcap > 0.0f ? 2.0f * LOG2E / opt.softcap : 0.0f, cap_l2e = opt.softcap * LOG2E;
     const int warp_tok_lo = min(ntok - 1, (warp * 16) / gp), warp_tok_hi = min(ntok - 1, (warp * 16 + 15) / gp);
     const bool warp_live = (warp * 16) / gp < ntok;
     const int warp_pos_lo = pos_first + warp_tok_lo, warp_pos_hi = pos_first + warp_tok_hi;
@@ -226,8 +238,10 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     float v = s_acc[j][e] * row_scale[e >> 1];
-                    if (opt.softcap > 0.0f) v = opt.softcap * tanhf(v / opt.softcap);
-                    v *= LOG2E;
+                    if (opt.softcap > 0.0f)      // cap tanh(v / cap) = cap (1 - 2 / (exp(2 v / cap) + 1))
+                        v = cap_l2e * fmaf(-2.0f, rcp_approx(ex2_approx(v * cap_arg) + 1.0f), 1.0f);
+                    else
+                        v *= LOG2E;
                     if (edge) {
                         const int key = key_lo + j * 8 + tq * 2 + (e & 1);
                         if (key > row_pos[e >> 1] || key < row_lo[e >> 1]) v = -INFINITY;
@@ -269,14 +283,9 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
             for (int kk = 0; kk < BN / 16; ++kk) {
                 unsigned pa[3][4];
 #pragma unroll
-                for (int x = 0; x < 4; ++x) {             // fragment register x: tile 2kk + (x >> 1), elements (x & 1) * 2, +1
-                    bf16 a0, b0, c0, a1, b1, c1;
-                    split3(s_acc[2 * kk + (x >> 1)][(x & 1) * 2], a0, b0, c0);
-                    split3(s_acc[2 * kk + (x >> 1)][(x & 1) * 2 + 1], a1, b1, c1);
-                    pa[0][x] = pack_bf16(a0, a1);
-                    pa[1][x] = pack_bf16(b0, b1);
-                    pa[2][x] = pack_bf16(c0, c1);
-                }
+                for (int x = 0; x < 4; ++x)               // fragment register x: tile 2kk + (x >> 1), elements (x & 1) * 2, +1
+                    split3_pair(s_acc[2 * kk + (x >> 1)][(x & 1) * 2], s_acc[2 * kk + (x >> 1)][(x & 1) * 2 + 1],
+                                pa[0][x], pa[1][x], pa[2][x]);
 #pragma unroll
                 for (int dp = 0; dp < NT_O / 2; ++dp) {
                     unsigned b[4];

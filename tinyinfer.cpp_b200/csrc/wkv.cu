@@ -6,7 +6,7 @@
 //    in the batch, or, for the first token that a request brings in this step, the row that the
 //    request's state kept from its last step (zeros for a new request).
 //  * wkv_recurrence: one block per (request, head) walks the request's tokens in order with the
-//    head's state S [d keys, d values] (float32, a column per thread, in registers):
+//    head's state S [d keys, d values] (float32, in registers, a column per four threads):
 //        decay_i = exp(-exp(a_i + w0_i)),  o_j = sum_i r_i (S_ij + u_i k_i v_j),
 //        S_ij <- decay_i S_ij + k_i v_j,
 //    then brings o to unit root mean square over the head, multiplies by a weight per element and
@@ -16,7 +16,7 @@
 //        xielu(z) = a_p z^2 + z/2 for z > 0, a_q (exp(z) - 1 - z) + z/2 otherwise.
 //
 // Everything that enters the recurrence is float32: r, k, v, the decay's argument, exponentials,
-// the state, the unit norm.  The sum over i runs in ascending order whatever the batch.
+// the state, the unit norm.  The order of the sum over i depends on nothing but d.
 #include "common.cuh"
 
 namespace {
@@ -41,65 +41,113 @@ token_shift_mix_kernel(const TH* h, const float* __restrict__ mu, int n_mix, int
     }
 }
 
+// Tokens are staged a tile (16 or 8) at a time: all threads fetch the tile's r, k, v, g and decays into shared
+// memory (the next tile's values are already in registers while this one is worked on), then the
+// tile's tokens follow one another without a barrier: column j of the state belongs to four
+// neighbouring lanes, lane part s holding its rows s, s + 4, s + 8, ...; the four partial sums of
+// o_j meet through two shuffles.  The unit norm of the tile's rows is taken afterwards, a warp per
+// token.
+constexpr int WKV_IS = 4;
+
 template <typename TH, typename TO, int DMAX>
-__global__ void __launch_bounds__(DMAX)
+__global__ void __launch_bounds__(DMAX * WKV_IS)
 wkv_recurrence_kernel(const float* r, const float* k, const float* v, const float* g, const float* a,
                       int in_stride, const float* __restrict__ w0, const float* __restrict__ u,
                       const float* __restrict__ norm_weight, float eps, const TH* h, int width,
                       const int* __restrict__ cu_q, const int* __restrict__ slots, float* state,
                       size_t state_stride, size_t prev_offset, int num_heads, int d,
                       TO* __restrict__ out) {
-    __shared__ float rs[2][DMAX], ks[2][DMAX], ws[2][DMAX], us[DMAX];
-    __shared__ float scratch[32];
-    const int req = blockIdx.x, head = blockIdx.y, j = threadIdx.x;
+    constexpr int WKV_TT = DMAX > 64 ? 8 : 16;           // tokens per staged tile (48 KB of shared memory at most)
+    constexpr int NI = DMAX / WKV_IS;                    // state rows per thread
+    constexpr int THREADS = DMAX * WKV_IS;
+    constexpr int PER = WKV_TT * DMAX / THREADS;         // staged elements of one array per thread
+    __shared__ __align__(16) float rs[WKV_TT][DMAX], ks[WKV_TT][DMAX], ws[WKV_TT][DMAX];
+    __shared__ float vs[WKV_TT][DMAX], gs[WKV_TT][DMAX], os[WKV_TT][DMAX], us[DMAX], inv_s[WKV_TT];
+    const int req = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+    const int j = tid / WKV_IS, part = tid % WKV_IS;
     const int t0 = cu_q[req], t1 = cu_q[req + 1];
     const bool live = j < d;
     float* slot = state + (size_t)slots[req] * state_stride;
     float* s_head = slot + (size_t)head * d * d;
-    float S[DMAX];
+    float S[NI];
 #pragma unroll
-    for (int i = 0; i < DMAX; ++i) S[i] = (live && i < d) ? s_head[(size_t)i * d + j] : 0.0f;
-    const int col = head * d + j;
-    const float w0j = live ? w0[col] : 0.0f, nw = live ? norm_weight[col] : 0.0f;
-    us[j] = live ? u[col] : 0.0f;
-    for (int t = t0; t < t1; ++t) {
-        const int b = (t - t0) & 1;
-        const size_t at = (size_t)t * in_stride + col;
-        float vj = 0.0f, gj = 0.0f;
-        if (live) {
-            rs[b][j] = r[at];
-            ks[b][j] = k[at];
-            ws[b][j] = expf(-expf(a[at] + w0j));
-            vj = v[at];
-            gj = g[at];
-        } else {
-            rs[b][j] = 0.0f; ks[b][j] = 0.0f; ws[b][j] = 0.0f;
+    for (int ii = 0; ii < NI; ++ii) {
+        const int i = part + WKV_IS * ii;
+        S[ii] = (live && i < d) ? s_head[(size_t)i * d + j] : 0.0f;
+    }
+    if (tid < DMAX) us[tid] = tid < d ? u[head * d + tid] : 0.0f;
+
+    float fr[PER], fk[PER], fa[PER], fv[PER], fg[PER];
+    auto fetch = [&](int tile0) {                        // the tile's values into registers
+#pragma unroll
+        for (int x = 0; x < PER; ++x) {
+            const int e = tid + x * THREADS, tt = e / DMAX, c = e % DMAX;
+            const bool ok = tile0 + tt < t1 && c < d;
+            const size_t at = (size_t)(tile0 + tt) * in_stride + head * d + c;
+            fr[x] = ok ? r[at] : 0.0f;
+            fk[x] = ok ? k[at] : 0.0f;
+            fa[x] = ok ? a[at] + w0[head * d + c] : 0.0f;
+            fv[x] = ok ? v[at] : 0.0f;
+            fg[x] = ok ? g[at] : 0.0f;
+        }
+    };
+    if (t0 < t1) fetch(t0);
+    for (int tile0 = t0; tile0 < t1; tile0 += WKV_TT) {
+        __syncthreads();                                 // the tile before has been read and written out
+#pragma unroll
+        for (int x = 0; x < PER; ++x) {
+            const int e = tid + x * THREADS, tt = e / DMAX, c = e % DMAX;
+            rs[tt][c] = fr[x];
+            ks[tt][c] = fk[x];
+            ws[tt][c] = expf(-expf(fa[x]));
+            vs[tt][c] = fv[x];
+            gs[tt][c] = fg[x];
         }
         __syncthreads();
-        float o = 0.0f;
+        if (tile0 + WKV_TT < t1) fetch(tile0 + WKV_TT);  // in flight while this tile is worked on
+        const int nt = min(WKV_TT, t1 - tile0);
+        for (int tt = 0; tt < nt; ++tt) {
+            const float vj = vs[tt][j];
+            float o = 0.0f;
 #pragma unroll
-        for (int i = 0; i < DMAX; ++i) {
-            if (i < d) {
-                const float kv = ks[b][i] * vj;
-                o = fmaf(rs[b][i], fmaf(us[i], kv, S[i]), o);
-                S[i] = fmaf(ws[b][i], S[i], kv);
+            for (int ii = 0; ii < NI; ++ii) {
+                const int i = part + WKV_IS * ii;
+                const float kv = ks[tt][i] * vj;
+                o = fmaf(rs[tt][i], fmaf(us[i], kv, S[ii]), o);
+                S[ii] = fmaf(ws[tt][i], S[ii], kv);
             }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (part == 0) os[tt][j] = live ? o : 0.0f;
         }
-        const float mean = block_sum(live ? o * o : 0.0f, scratch) / (float)d;
-        if (live) {
-            const float y = o * (1.0f / sqrtf(mean + eps)) * nw * (gj / (1.0f + expf(-gj)));
-            out[(size_t)t * num_heads * d + col] = from_f32<TO>(y);
+        __syncthreads();
+        for (int tt = tid / 32; tt < nt; tt += THREADS / 32) {       // a warp per token: its unit norm
+            float ss = 0.0f;
+            for (int c = tid % 32; c < d; c += 32) ss = fmaf(os[tt][c], os[tt][c], ss);
+            ss = warp_sum(ss);
+            if (tid % 32 == 0) inv_s[tt] = 1.0f / sqrtf(ss / (float)d + eps);
+        }
+        __syncthreads();
+        for (int e = tid; e < nt * DMAX; e += THREADS) {
+            const int tt = e / DMAX, c = e % DMAX;
+            if (c < d) {
+                const float gj = gs[tt][c];
+                const float y = os[tt][c] * inv_s[tt] * norm_weight[head * d + c] * (gj / (1.0f + expf(-gj)));
+                out[(size_t)(tile0 + tt) * num_heads * d + head * d + c] = from_f32<TO>(y);
+            }
         }
     }
     if (t1 > t0) {
         if (live) {
 #pragma unroll
-            for (int i = 0; i < DMAX; ++i)
-                if (i < d) s_head[(size_t)i * d + j] = S[i];
+            for (int ii = 0; ii < NI; ++ii) {
+                const int i = part + WKV_IS * ii;
+                if (i < d) s_head[(size_t)i * d + j] = S[ii];
+            }
         }
         if (head == 0) {
             const TH* last = h + (size_t)(t1 - 1) * width;
-            for (int e = j; e < width; e += blockDim.x) slot[prev_offset + e] = to_f32(last[e]);
+            for (int e = tid; e < width; e += THREADS) slot[prev_offset + e] = to_f32(last[e]);
         }
     }
 }
@@ -150,7 +198,7 @@ extern "C" int ti_wkv_recurrence(const float* r, const float* k, const float* v,
     dim3 grid(num_requests, num_heads);
     cudaStream_t s = (cudaStream_t)stream;
 #define LAUNCH(TH, DMAX)                                                                           \
-    wkv_recurrence_kernel<TH, TH, DMAX><<<grid, DMAX, 0, s>>>(                                       \
+    wkv_recurrence_kernel<TH, TH, DMAX><<<grid, DMAX * WKV_IS, 0, s>>>(                                       \
         r, k, v, g, a, in_stride, w0, u, norm_weight, eps, (const TH*)h, width, cu_q, slots, state,    \
         (size_t)state_stride, (size_t)prev_offset, num_heads, d, (TH*)out)
 #define CALL(TH)                                                                                   \
