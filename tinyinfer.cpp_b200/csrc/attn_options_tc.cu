@@ -14,8 +14,10 @@
 // position; masks are applied only in tiles that touch an edge.  Queries lie in shared memory
 // (a row of queries may be wide: a latent row), the head size is a runtime multiple of 16.
 // A block makes DVS of the value columns; wider values are cut into slices, a block each.
-// Few rows (decoding) cut the keys of a tile into runs, a block each, whose unnormalised
-// results a second launch adds (attn_options_merge).
+// Few rows (decoding) cut the keys of a row into runs of tiles, a block each, whose unnormalised
+// results a second launch adds (attn_options_merge); and when a tile has at most 16 rows (single
+// tokens, up to 16 heads per kv head) the four warps of a block share those rows and take a
+// quarter of every tile's keys each, meeting in shared memory at the end.
 //
 // Precision.  Scores, cap (with the hardware's float32 exponential and reciprocal, relative error
 // about 2^-22), softmax weights and sums are float32.  The weighted sum of the values
@@ -96,7 +98,11 @@ __device__ __forceinline__ int first_visible(int p, const TcOptions& o) {
 }
 
 // tiles[i] = {request row, first flat token, tokens (<= 64 / gp)}
-template <int DVS>
+// MODE 0: the warps of a block have 16 rows each.  MODE 1 (KS): all have the same 16 rows and a quarter
+// of a tile's keys.  MODE 2 (shared rows, at most 16 live rows, up to four slices of value columns):
+// all have the same 16 rows and all keys, and warp w makes slice w of the value columns, so that a
+// tile of rows is fetched once for all of them.
+template <int DVS, int MODE>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* __restrict__ positions,
                        const int* __restrict__ block_table, int bt_stride, const bf16* pages, int num_pages,
@@ -104,7 +110,10 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
                        int nsplit, TcOptions opt, bf16* __restrict__ out, float* __restrict__ part_o,
                        float* __restrict__ part_ml, int* __restrict__ status) {
     constexpr int NT_O = DVS / 8;
+    constexpr bool KS = MODE == 1;
     constexpr int V_ROW = DVS * 2 + 16;
+    // KS (at most 16 live rows, decoding): every warp has the same 16 rows and a quarter of a tile's keys
+    constexpr int NJ = KS ? BN / 32 : BN / 8;            // 8-key columns of a tile that a warp multiplies
     extern __shared__ __align__(16) unsigned char smem[];
     const int k_row = dk * 2 + 16;                       // bytes of a staged query or key row
     const int stage_bytes = BN * k_row + (opt.shared_rows ? 0 : BN * V_ROW);
@@ -112,9 +121,10 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
     unsigned char* ring = smem + BM * k_row;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tq = lane & 3;
-    const int slices = dv / DVS;
+    const int rbase = MODE == 0 ? warp * 16 : 0, kbase = KS ? warp * 16 : 0;
+    const int slices = MODE == 2 ? 1 : dv / DVS;         // slices that the grid spreads over blocks
     int bx = blockIdx.x;
-    const int slice = bx % slices; bx /= slices;
+    const int slice = MODE == 2 ? warp : bx % slices; bx /= slices;
     const int hb = bx % head_blocks; const int kvh = bx / head_blocks;
     const int group = num_heads / num_kv_heads;
     const int tile_id = blockIdx.y, split = blockIdx.z;
@@ -142,15 +152,15 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
     float row_scale[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-        const int i = warp * 16 + g + 8 * r;
+        const int i = rbase + g + 8 * r;
         row_h[r] = row_head(i);
         row_pos[r] = row_h[r] >= 0 ? pos_first + row_token(i) : -1;
         row_lo[r] = row_h[r] >= 0 ? first_visible(row_pos[r], opt) : 0;
         row_scale[r] = opt.scale * ((opt.head_scale && row_h[r] >= 0) ? opt.head_scale[row_h[r]] : 1.0f);
     }
     const float cap_arg = opt.softcap > 0.0f ? 2.0f * LOG2E / opt.softcap : 0.0f, cap_l2e = opt.softcap * LOG2E;
-    const int warp_tok_lo = min(ntok - 1, (warp * 16) / gp), warp_tok_hi = min(ntok - 1, (warp * 16 + 15) / gp);
-    const bool warp_live = (warp * 16) / gp < ntok;
+    const int warp_tok_lo = min(ntok - 1, rbase / gp), warp_tok_hi = min(ntok - 1, (rbase + 15) / gp);
+    const bool warp_live = rbase / gp < ntok && (MODE != 2 || warp < dv / DVS);
     const int warp_pos_lo = pos_first + warp_tok_lo, warp_pos_hi = pos_first + warp_tok_hi;
     const int warp_lo_first = first_visible(warp_pos_lo, opt), warp_lo_last = first_visible(warp_pos_hi, opt);
 
@@ -208,23 +218,23 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        const int key_lo = kt * BN, key_hi = key_lo + BN - 1;
+        const int key_lo = kt * BN + kbase, key_hi = key_lo + NJ * 8 - 1;     // the warp's keys of the tile
         const bool visible = warp_live && key_lo <= warp_pos_hi && key_hi >= warp_lo_first;
         if (visible) {
             const unsigned char* ks = ring + (size_t)stage * stage_bytes;
             const unsigned char* vs = opt.shared_rows ? ks + (size_t)slice * DVS * 2 : ks + BN * k_row;
             const int v_row = opt.shared_rows ? k_row : V_ROW;
-            float s_acc[BN / 8][4];
+            float s_acc[NJ][4];
 #pragma unroll
-            for (int j = 0; j < BN / 8; ++j) s_acc[j][0] = s_acc[j][1] = s_acc[j][2] = s_acc[j][3] = 0.0f;
+            for (int j = 0; j < NJ; ++j) s_acc[j][0] = s_acc[j][1] = s_acc[j][2] = s_acc[j][3] = 0.0f;
             for (int kk = 0; kk < ksteps; ++kk) {
                 unsigned qa[4];
-                ldmatrix_x4(qa, q_s + (size_t)(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * k_row
+                ldmatrix_x4(qa, q_s + (size_t)(rbase + (lane & 7) + ((lane >> 3) & 1) * 8) * k_row
                                     + (kk * 16 + (lane >> 4) * 8) * 2);
 #pragma unroll
-                for (int jp = 0; jp < BN / 16; ++jp) {
+                for (int jp = 0; jp < NJ / 2; ++jp) {
                     unsigned b[4];
-                    const int key = jp * 16 + (lane >> 4) * 8 + (lane & 7);
+                    const int key = kbase + jp * 16 + (lane >> 4) * 8 + (lane & 7);
                     const int dim = kk * 16 + ((lane >> 3) & 1) * 8;
                     ldmatrix_x4(b, ks + (size_t)key * k_row + dim * 2);
                     mma_bf16(s_acc[2 * jp], qa, b[0], b[1]);
@@ -234,7 +244,7 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
             const bool edge = key_hi > warp_pos_lo || key_lo < warp_lo_last;
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int j = 0; j < BN / 8; ++j) {
+            for (int j = 0; j < NJ; ++j) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     float v = s_acc[j][e] * row_scale[e >> 1];
@@ -262,7 +272,7 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
             }
             float sum[2] = {0.0f, 0.0f};
 #pragma unroll
-            for (int j = 0; j < BN / 8; ++j) {
+            for (int j = 0; j < NJ; ++j) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const float p = exp2f(s_acc[j][e] - m_use[e >> 1]);
@@ -280,7 +290,7 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
                 }
             }
 #pragma unroll
-            for (int kk = 0; kk < BN / 16; ++kk) {
+            for (int kk = 0; kk < NJ / 2; ++kk) {
                 unsigned pa[3][4];
 #pragma unroll
                 for (int x = 0; x < 4; ++x)               // fragment register x: tile 2kk + (x >> 1), elements (x & 1) * 2, +1
@@ -289,7 +299,7 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
 #pragma unroll
                 for (int dp = 0; dp < NT_O / 2; ++dp) {
                     unsigned b[4];
-                    const int key = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                    const int key = kbase + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
                     const int dim = dp * 16 + (lane >> 4) * 8;
                     ldmatrix_x4_trans(b, vs + (size_t)key * v_row + dim * 2);
 #pragma unroll
@@ -308,11 +318,61 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
+    if (KS) {
+        // the four warps hold the same rows over different keys: their maxima, sums and outputs
+        // meet in shared memory (the ring is free now), and every thread finishes some elements
+        float* m_s = reinterpret_cast<float*>(ring);          // [4][16]
+        float* l_s = m_s + WARPS * 16;                        // [4][16]
+        float* o_s = l_s + WARPS * 16;                        // [4][16][DVS]
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = g + 8 * r;
+            if (tq == 0) { m_s[warp * 16 + row] = m_run[r]; l_s[warp * 16 + row] = l_run[r]; }
+#pragma unroll
+            for (int x = 0; x < NT_O; ++x) {
+                o_s[(warp * 16 + row) * DVS + x * 8 + tq * 2] = o[x][2 * r];
+                o_s[(warp * 16 + row) * DVS + x * 8 + tq * 2 + 1] = o[x][2 * r + 1];
+            }
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < 16 * DVS; e += WARPS * 32) {
+            const int row = e / DVS, col = e % DVS;
+            const int h = row_head(row);
+            if (h < 0) continue;
+            const int t = tok0 + row_token(row);
+            float m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) m = fmaxf(m, m_s[w * 16 + row]);
+            float l = 0.0f, acc = 0.0f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float mw = m_s[w * 16 + row];
+                const float f = mw == -INFINITY ? 0.0f : exp2f(mw - m);
+                l = fmaf(l_s[w * 16 + row], f, l);
+                acc = fmaf(o_s[(w * 16 + row) * DVS + col], f, acc);
+            }
+            if (nsplit > 1) {
+                const size_t at = ((size_t)t * num_heads + h) * nsplit + split;
+                part_o[at * dv + slice * DVS + col] = acc;
+                if (col == 0 && slice == 0) { part_ml[at * 2] = m; part_ml[at * 2 + 1] = l; }
+                continue;
+            }
+            if (opt.sink) l += exp2f(opt.sink[h] * LOG2E - m);
+            acc /= l;
+            if (opt.gate) {
+                const float* gt = opt.gate + (size_t)t * opt.gate_stride;
+                const float gv = opt.gate_per_head ? gt[h] : gt[(size_t)h * dv + slice * DVS + col];
+                acc *= 1.0f / (1.0f + expf(-gv));
+            }
+            out[((size_t)t * num_heads + h) * dv + slice * DVS + col] = __float2bfloat16_rn(acc);
+        }
+        return;
+    }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int h = row_h[r];
         if (h < 0) continue;
-        const int t = tok0 + row_token(warp * 16 + g + 8 * r);
+        const int t = tok0 + row_token(rbase + g + 8 * r);
         if (nsplit > 1) {                             // unnormalised, for the merging launch
             const size_t at = ((size_t)t * num_heads + h) * nsplit + split;
             float* po = part_o + at * dv + slice * DVS + tq * 2;
@@ -340,30 +400,39 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
     }
 }
 
-// adds the runs of a row's keys: one warp per (token of the list, head)
+// adds the runs of a row's keys: blocks of 128 value columns of a (token, head); the runs' factors are made once,
+// and a thread has several loads in flight
 __global__ void __launch_bounds__(128)
-attn_options_merge_kernel(const float* part_o, const float* part_ml, int nsplit, int num_items, int num_heads,
-                          int dv, const float* __restrict__ sink, const float* gate, int gate_stride,
-                          int gate_per_head, bf16* __restrict__ out) {
-    const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (item >= num_items) return;
-    const int t = item / num_heads, h = item % num_heads;
+attn_options_merge_kernel(const float* part_o, const float* part_ml, int nsplit, int num_heads, int dv,
+                          const float* __restrict__ sink, const float* gate, int gate_stride, int gate_per_head,
+                          bf16* __restrict__ out) {
+    __shared__ float f_s[64];
+    __shared__ float inv_s;
+    const int item = blockIdx.x, t = item / num_heads, h = item % num_heads;
     const float* ml = part_ml + (size_t)item * nsplit * 2;
-    float m = -INFINITY;
-    for (int z = 0; z < nsplit; ++z) m = fmaxf(m, ml[z * 2]);
-    float l = sink ? exp2f(sink[h] * LOG2E - m) : 0.0f;
-    for (int z = 0; z < nsplit; ++z) l += ml[z * 2 + 1] * (ml[z * 2] == -INFINITY ? 0.0f : exp2f(ml[z * 2] - m));
-    float inv = 1.0f / l;
-    const float* gt = gate ? gate + (size_t)t * gate_stride : nullptr;
-    if (gt && gate_per_head) inv *= 1.0f / (1.0f + expf(-gt[h]));
-    for (int d = lane; d < dv; d += 32) {
-        float acc = 0.0f;
-        for (int z = 0; z < nsplit; ++z) {
-            const float w = ml[z * 2] == -INFINITY ? 0.0f : exp2f(ml[z * 2] - m);
-            acc = fmaf(part_o[((size_t)item * nsplit + z) * dv + d], w, acc);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const float m0 = lane < nsplit ? ml[lane * 2] : -INFINITY, m1 = lane + 32 < nsplit ? ml[(lane + 32) * 2] : -INFINITY;
+        const float m = warp_max(fmaxf(m0, m1));
+        const float f0 = m0 == -INFINITY ? 0.0f : exp2f(m0 - m), f1 = m1 == -INFINITY ? 0.0f : exp2f(m1 - m);
+        float l = (lane < nsplit ? ml[lane * 2 + 1] * f0 : 0.0f) + (lane + 32 < nsplit ? ml[(lane + 32) * 2 + 1] * f1 : 0.0f);
+        l = warp_sum(l);
+        if (sink) l += exp2f(sink[h] * LOG2E - m);
+        f_s[lane] = f0; f_s[lane + 32] = f1;
+        if (lane == 0) {
+            float inv = 1.0f / l;
+            if (gate && gate_per_head) inv *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + h]));
+            inv_s = inv;
         }
-        acc *= inv;
-        if (gt && !gate_per_head) acc *= 1.0f / (1.0f + expf(-gt[(size_t)h * dv + d]));
+    }
+    __syncthreads();
+    const float* po = part_o + (size_t)item * nsplit * dv;
+    for (int d = blockIdx.y * 128 + threadIdx.x; d < dv; d += 128 * gridDim.y) {
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int z = 0; z < nsplit; ++z) acc = fmaf(po[(size_t)z * dv + d], f_s[z], acc);
+        acc *= inv_s;
+        if (gate && !gate_per_head) acc *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + (size_t)h * dv + d]));
         out[(size_t)item * dv + d] = __float2bfloat16_rn(acc);
     }
 }
@@ -372,7 +441,9 @@ int value_slice(int dv) { return dv % 128 == 0 ? 128 : dv % 64 == 0 ? 64 : dv % 
 
 size_t smem_bytes(int dk, int dv, int shared_rows) {
     const size_t k_row = (size_t)dk * 2 + 16, v_row = (size_t)value_slice(dv) * 2 + 16;
-    return BM * k_row + STAGES * (BN * k_row + (shared_rows ? 0 : BN * v_row));
+    const size_t ring = STAGES * (BN * k_row + (shared_rows ? 0 : BN * v_row));
+    const size_t meet = (size_t)WARPS * 16 * (value_slice(dv) + 2) * sizeof(float);     // where split warps meet
+    return BM * k_row + (ring > meet ? ring : meet);
 }
 
 }  // namespace
@@ -392,14 +463,16 @@ extern "C" int ti_attn_options_tc_group_rows(int num_heads, int num_kv_heads) {
 
 // tiles: int32 [num_tiles, 3] = {request row, first flat token, tokens}; a tile has at most
 // 64 / group_rows consecutive tokens of one request.  part_o/part_ml: float32 scratch of
-// [tokens, heads, nsplit, dv] and [tokens, heads, nsplit, 2] when nsplit > 1.
+// [tokens, heads, nsplit, dv] and [tokens, heads, nsplit, 2] when nsplit > 1.  key_split: every tile has at
+// most 16 rows (tokens x group_rows), and the warps of a block share them and split a tile's keys (1) or,
+// with shared rows, the slices of the value columns (2).
 extern "C" int ti_attn_options_tc(const void* q, const int* tiles, int num_tiles, int num_tokens,
                                   const int* positions, const int* block_table, int bt_stride, const void* pages,
                                   int num_pages, int page_size, int num_heads, int num_kv_heads, int dk, int dv,
                                   int shared_rows, int window, int chunk, float scale, float softcap,
                                   const float* head_scale, const float* sink, const float* gate, int gate_stride,
-                                  int gate_per_head, int nsplit, float* part_o, float* part_ml, void* out,
-                                  int* status, void* stream) {
+                                  int gate_per_head, int nsplit, float* part_o, float* part_ml, int key_split,
+                                  void* out, int* status, void* stream) {
     if (num_tiles == 0) return 0;
     TI_REQUIRE(num_heads % num_kv_heads == 0, "attn_options_tc: %d heads over %d kv heads", num_heads, num_kv_heads);
     TI_REQUIRE(ti_attn_options_tc_supported(dk, dv, page_size, shared_rows),
@@ -407,41 +480,45 @@ extern "C" int ti_attn_options_tc(const void* q, const int* tiles, int num_tiles
                "(a multiple of 16) are not supported", dk, dv, page_size);
     TI_REQUIRE(nsplit >= 1 && nsplit <= 64 && (nsplit == 1 || (part_o && part_ml)), "attn_options_tc: runs and scratch");
     TI_REQUIRE(num_tiles <= 65535, "attn_options_tc: %d tiles exceed the grid limit", num_tiles);
+    TI_REQUIRE(!key_split || ti_attn_options_tc_group_rows(num_heads, num_kv_heads) <= 16,
+               "attn_options_tc: warps split the keys only when a tile has at most 16 rows");
     const int gp = ti_attn_options_tc_group_rows(num_heads, num_kv_heads);
     const int group = num_heads / num_kv_heads, head_blocks = (group + gp - 1) / gp;
     const int dvs = value_slice(dv);
     const size_t smem = smem_bytes(dk, dv, shared_rows);
     TcOptions opt = {window, chunk, scale, softcap, head_scale, sink, gate, gate_stride, gate_per_head, shared_rows};
-    dim3 grid(num_kv_heads * head_blocks * (dv / dvs), num_tiles, nsplit);
+    TI_REQUIRE(key_split != 2 || (shared_rows && dv / dvs <= WARPS), "attn_options_tc: a warp per slice needs shared rows "
+               "and at most %d slices", WARPS);
+    dim3 grid(num_kv_heads * head_blocks * (key_split == 2 ? 1 : dv / dvs), num_tiles, nsplit);
     cudaStream_t s = (cudaStream_t)stream;
-#define LAUNCH(DVS)                                                                                       \
+#define LAUNCH(DVS, MODE)                                                                                       \
     {                                                                                                     \
         static TiPerDevice configured;                                                                    \
         static size_t allowed = 0;                                                                        \
         if (configured.first_use() || smem > allowed) {                                                   \
-            cudaError_t e = cudaFuncSetAttribute(attn_options_tc_kernel<DVS>,                             \
+            cudaError_t e = cudaFuncSetAttribute(attn_options_tc_kernel<DVS, MODE>,                             \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); \
             if (e != cudaSuccess) return ti_fail("attn_options_tc: %s", cudaGetErrorString(e));           \
             configured.mark();                                                                            \
             allowed = 227 * 1024;                                                                         \
         }                                                                                                 \
-        attn_options_tc_kernel<DVS><<<grid, WARPS * 32, smem, s>>>(                                        \
+        attn_options_tc_kernel<DVS, MODE><<<grid, WARPS * 32, smem, s>>>(                                        \
             (const bf16*)q, tiles, positions, block_table, bt_stride, (const bf16*)pages, num_pages,       \
             page_size, num_heads, num_kv_heads, dk, dv, gp, head_blocks, nsplit, opt, (bf16*)out, part_o,   \
             part_ml, status);                                                                             \
     }
     switch (dvs) {
-        case 128: LAUNCH(128); break;
-        case 64: LAUNCH(64); break;
-        case 32: LAUNCH(32); break;
-        default: LAUNCH(16); break;
+        case 128: if (key_split == 2) LAUNCH(128, 2) else if (key_split) LAUNCH(128, 1) else LAUNCH(128, 0) break;
+        case 64: if (key_split == 2) LAUNCH(64, 2) else if (key_split) LAUNCH(64, 1) else LAUNCH(64, 0) break;
+        case 32: if (key_split == 2) LAUNCH(32, 2) else if (key_split) LAUNCH(32, 1) else LAUNCH(32, 0) break;
+        default: if (key_split == 2) LAUNCH(16, 2) else if (key_split) LAUNCH(16, 1) else LAUNCH(16, 0) break;
     }
 #undef LAUNCH
     if (int rc = ti_check_launch("attn_options_tc")) return rc;
     if (nsplit > 1) {
         const int items = num_tokens * num_heads;
-        attn_options_merge_kernel<<<(items + 3) / 4, 128, 0, s>>>(part_o, part_ml, nsplit, items, num_heads, dv, sink,
-                                                                 gate, gate_stride, gate_per_head, (bf16*)out);
+        attn_options_merge_kernel<<<dim3(items, (dv + 127) / 128), 128, 0, s>>>(part_o, part_ml, nsplit, num_heads, dv, sink, gate, gate_stride,
+                                                       gate_per_head, (bf16*)out);
         return ti_check_launch("attn_options_merge");
     }
     return 0;

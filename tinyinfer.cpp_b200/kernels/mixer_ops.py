@@ -65,7 +65,7 @@ class MixerOps:
             b.ti_attn_options_tc_supported.argtypes = [_i, _i, _i, _i]
             b.ti_attn_options_tc_group_rows.argtypes = [_i, _i]
             b.ti_attn_options_tc.argtypes = [_vp, _vp, _i, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i,
-                                             _f, _f, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]
+                                             _f, _f, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp]
             self._mixers_tc = b
         return self._mixers_tc
 
@@ -211,8 +211,12 @@ class MixerOps:
             # count depends on the step's shape and the model's bounds alone
             nsplit, part_o, part_ml = 1, None, None
             slices = dv // (128 if dv % 128 == 0 else 64 if dv % 64 == 0 else 32 if dv % 32 == 0 else 16)
-            blocks = tiles.shape[0] * num_kv_heads * -(-(num_heads // num_kv_heads) // gp) * slices
-            if getattr(step, "max_q_len", 0) == 1 and blocks < 2 * self.num_sms:
+            single = getattr(step, "max_q_len", 0) == 1
+            # single tokens of few heads: the warps of a block share the rows and split the keys (1) or,
+            # over shared rows, the slices of the value columns (2)
+            mode = 0 if not (single and gp <= 16) else 2 if (shared_rows and 1 < slices <= 4) else 1
+            blocks = tiles.shape[0] * num_kv_heads * -(-(num_heads // num_kv_heads) // gp) * (1 if mode == 2 else slices)
+            if single and blocks < 2 * self.num_sms:
                 most = step.max_position or step.max_ctx_len
                 for bound in (window, chunk):
                     if bound:
@@ -227,7 +231,8 @@ class MixerOps:
                 bt.stride(0), pages.data_ptr(), pages.shape[0], cache.page_size, num_heads, num_kv_heads, dk, dv,
                 int(bool(shared_rows)), int(window or 0), int(chunk or 0), float(scale), float(softcap or 0.0),
                 _ptr(head_scale), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0,
-                int(bool(gate_per_head)), nsplit, _ptr(part_o), _ptr(part_ml), out.data_ptr(),
+                int(bool(gate_per_head)), nsplit, _ptr(part_o), _ptr(part_ml),
+                mode, out.data_ptr(),
                 self.status.data_ptr(), self._stream()), self.mixers_tc)
             return
         self._mx(self.mixers.ti_attention_options(
