@@ -296,16 +296,23 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
                 for (int x = 0; x < 4; ++x)               // fragment register x: tile 2kk + (x >> 1), elements (x & 1) * 2, +1
                     split3_pair(s_acc[2 * kk + (x >> 1)][(x & 1) * 2], s_acc[2 * kk + (x >> 1)][(x & 1) * 2 + 1],
                                 pa[0][x], pa[1][x], pa[2][x]);
+                // value fragments of up to four column pairs at a time, so that the products into one
+                // accumulator stand eight apart
+                constexpr int DPG = NT_O / 2 < 4 ? NT_O / 2 : 4;
 #pragma unroll
-                for (int dp = 0; dp < NT_O / 2; ++dp) {
-                    unsigned b[4];
+                for (int dp0 = 0; dp0 < NT_O / 2; dp0 += DPG) {
+                    unsigned b[DPG][4];
                     const int key = kbase + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
-                    const int dim = dp * 16 + (lane >> 4) * 8;
-                    ldmatrix_x4_trans(b, vs + (size_t)key * v_row + dim * 2);
+#pragma unroll
+                    for (int x = 0; x < DPG; ++x)
+                        ldmatrix_x4_trans(b[x], vs + (size_t)key * v_row + ((dp0 + x) * 16 + (lane >> 4) * 8) * 2);
 #pragma unroll
                     for (int part = 2; part >= 0; --part) {       // the smallest parts first
-                        mma_bf16(o[2 * dp], pa[part], b[0], b[1]);
-                        mma_bf16(o[2 * dp + 1], pa[part], b[2], b[3]);
+#pragma unroll
+                        for (int x = 0; x < DPG; ++x) {
+                            mma_bf16(o[2 * (dp0 + x)], pa[part], b[x][0], b[x][1]);
+                            mma_bf16(o[2 * (dp0 + x) + 1], pa[part], b[x][2], b[x][3]);
+                        }
                     }
                 }
             }
