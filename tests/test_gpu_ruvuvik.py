@@ -86,6 +86,22 @@ def test_activations(ops, dtype):
     assert (out.cpu().double() - torch.tanh(z.double())).abs().max() < tol
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sizes", [(1, 96, 64), (8, 320, 256), (33, 130, 64), (64, 256, 96), (200, 192, 128), (5, 40, 24)])
+def test_product_with_activation(ops, sizes, dtype):
+    """Few rows take the product whose epilogue applies the activation, many rows (and sizes that
+    product does not take) the product followed by the row-wise kernel: the same numbers."""
+    m, n, k = sizes
+    g = torch.Generator().manual_seed(m)
+    h = torch.randn((m, k), generator=g).to(dtype)
+    w = (torch.randn((n, k), generator=g) * 2 / k ** 0.5).to(torch.bfloat16)
+    out = torch.empty((m, n), dtype=dtype, device=DEV)
+    ops.linear_xielu(h.to(DEV), w.to(DEV), plain.softplus(0.4), 0.5 + plain.softplus(-0.3), out)
+    want = plain.xielu(h.double() @ w.double().T, 0.4, -0.3)
+    err = ((out.cpu().double() - want).abs() / (1 + want.abs())).max()
+    assert err < (2e-5 if dtype == torch.float32 else 1e-2), err
+
+
 def _paged(ctx_lens, q_lens, page_size, row_elems, dtype, seed=0):
     """A step of requests with ``ctx_lens[r]`` tokens of which the last ``q_lens[r]`` are new, over
     scrambled pages of ``row_elems`` elements per token."""
@@ -334,6 +350,27 @@ def test_each_mixer_alone_in_portions(ops, kind, m, dtype):
         want = fn(x.to(dtype).double(), w64, "x.", m, 1e-5)[0]
         err = (got[r].double() - want).abs().max() / want.abs().max()
         assert err < (2e-5 if dtype == torch.float32 else 3e-2), f"{kind} request {r}: {err}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m", [dict(heads=2, dim=12), dict(heads=1, dim=64), dict(heads=3, dim=40), dict(heads=1, dim=128)])
+def test_recurrence_over_long_portions(ops, m, dtype):
+    """Portions long enough that a head's state columns are cut over several blocks, between portions
+    that are not: the state passes from one form of the kernel to the other."""
+    from tinyinfer_b200.parts.wkv import WkvMixer
+    width = 64
+    g = torch.Generator().manual_seed(m["dim"])
+    w = mixer_weights("wkv", m, width, g, decay_rank=6)
+    part = WkvMixer(width, m["heads"], m["dim"], 1e-5)
+    part.load_weights({k: v.to(DEV) for k, v in w.items()}, ops)
+    inputs = {"a": torch.randn((203, width), generator=g), "b": torch.randn((72, width), generator=g)}
+    cuts = [[("a", 3)], [("a", 130)], [("a", 1), ("b", 70)], [("a", 69), ("b", 2)]]
+    got = _run_mixer(ops, part, inputs, cuts, dtype)
+    w64 = {"x." + k: v.double() for k, v in w.items()}
+    for r, x in inputs.items():
+        want = plain.wkv(x.to(dtype).double(), w64, "x.", m, 1e-5)[0]
+        err = (got[r].double() - want).abs().max() / want.abs().max()
+        assert err < (2e-5 if dtype == torch.float32 else 3e-2), f"request {r}: {err}"
 
 
 # ---- the model through the engine ------------------------------------------------------------

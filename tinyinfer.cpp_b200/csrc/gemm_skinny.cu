@@ -20,7 +20,7 @@ constexpr int WARPS = 8;
 constexpr int STRIP = 16;
 constexpr int CHUNK = 32;
 
-enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SWIGLU = 2 };
+enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SWIGLU = 2, MODE_XIELU = 3 };
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
     uint4 v;
@@ -48,7 +48,7 @@ template <int NT, int ROWS, int BATCH, bool STORE_ONLY = false>
 __global__ void __launch_bounds__(WARPS * 32, BATCH == 4 && NT == 1 ? 3 : 2)
 gemm_skinny_kernel(const bf16* a, const bf16* __restrict__ w, float* __restrict__ c,
                    bf16* __restrict__ out_act, int m, int n, int k, int lda, int ldw, int ldc,
-                   int ld_act, int mode) {
+                   int ld_act, int mode, float act_p, float act_q) {
     constexpr int MP = NT * 8;                                  // padded token count
     __shared__ float part[WARPS][ROWS][MP + 1];
     if (STORE_ONLY) mode = MODE_STORE;
@@ -170,7 +170,12 @@ gemm_skinny_kernel(const bf16* a, const bf16* __restrict__ w, float* __restrict_
             float sum = 0.0f;
 #pragma unroll
             for (int wp = 0; wp < WARPS; ++wp) sum += part[wp][i][tok];
-            if (n0 + i < n) c[(size_t)tok * ldc + n0 + i] = mode == MODE_ACCUMULATE ? old_c[it] + sum : sum;
+            if (mode == MODE_XIELU) {          // act_p z^2 + z/2 above zero, act_q (exp(z) - 1 - z) + z/2 below
+                const float y = sum > 0.0f ? fmaf(act_p * sum, sum, 0.5f * sum) : fmaf(act_q, expm1f(sum) - sum, 0.5f * sum);
+                if (n0 + i < n) out_act[(size_t)tok * ld_act + n0 + i] = __float2bfloat16_rn(y);
+            } else if (n0 + i < n) {
+                c[(size_t)tok * ldc + n0 + i] = mode == MODE_ACCUMULATE ? old_c[it] + sum : sum;
+            }
         }
     }
 }
@@ -181,9 +186,10 @@ extern "C" int ti_gemm_skinny_supported(int m, int n, int k, int lda, int ldw) {
     return m >= 1 && m <= 64 && n >= 1 && k >= CHUNK && k % CHUNK == 0 && lda % 8 == 0 && ldw % 8 == 0;
 }
 
-// mode 0: c = a w^T; 1: c += a w^T; 2: out_act[m, n/2] = swiglu over strips of 8 gate + 8 up rows.
-extern "C" int ti_gemm_skinny(const void* a, const void* w, float* c, void* out_act, int m, int n,
-                              int k, int lda, int ldw, int ldc, int ld_act, int mode, void* stream) {
+// mode 0: c = a w^T; 1: c += a w^T; 2: out_act[m, n/2] = swiglu over strips of 8 gate + 8 up rows;
+// 3: out_act[m, n] = xielu(a w^T) with the activation's two factors.
+static int skinny(const void* a, const void* w, float* c, void* out_act, int m, int n, int k, int lda, int ldw,
+                  int ldc, int ld_act, int mode, float act_p, float act_q, void* stream) {
     if (m == 0 || n == 0) return 0;
     TI_REQUIRE(ti_gemm_skinny_supported(m, n, k, lda, ldw),
                "gemm_skinny: M=%d (1..64), K=%d (multiple of 32) or row strides %d, %d (multiples of 8) "
@@ -198,23 +204,35 @@ extern "C" int ti_gemm_skinny(const void* a, const void* w, float* c, void* out_
     if (narrow)                                                                                     \
         ti_launch_pdl(gemm_skinny_kernel<NT, 8, 8>, (unsigned)((n + 7) / 8), WARPS * 32, 0, s,      \
                       (const bf16*)a, (const bf16*)w, c, (bf16*)out_act, m, n, k, lda, ldw, ldc,    \
-                      ld_act, mode);                                                                \
+                      ld_act, mode, act_p, act_q);                                                                \
     else if (k <= SHORT_K && mode == MODE_STORE && NT <= 2)                                         \
         ti_launch_pdl((gemm_skinny_kernel<NT <= 2 ? NT : 1, 16, 4, true>), (unsigned)((n + STRIP - 1) / STRIP), \
                       WARPS * 32, 0, s, (const bf16*)a, (const bf16*)w, c, (bf16*)out_act, m, n, k, \
-                      lda, ldw, ldc, ld_act, mode);                                                 \
+                      lda, ldw, ldc, ld_act, mode, act_p, act_q);                                   \
     else if (k <= SHORT_K)                                                                          \
         ti_launch_pdl(gemm_skinny_kernel<NT, 16, 4>, (unsigned)((n + STRIP - 1) / STRIP),           \
                       WARPS * 32, 0, s, (const bf16*)a, (const bf16*)w, c, (bf16*)out_act, m, n, k, \
-                      lda, ldw, ldc, ld_act, mode);                                                 \
+                      lda, ldw, ldc, ld_act, mode, act_p, act_q);                                   \
     else                                                                                            \
         ti_launch_pdl(gemm_skinny_kernel<NT, 16, 8>, (unsigned)((n + STRIP - 1) / STRIP),           \
                       WARPS * 32, 0, s, (const bf16*)a, (const bf16*)w, c, (bf16*)out_act, m, n, k, \
-                      lda, ldw, ldc, ld_act, mode)
+                      lda, ldw, ldc, ld_act, mode, act_p, act_q)
     if (m <= 8) { LAUNCH(1); }
     else if (m <= 16) { LAUNCH(2); }
     else if (m <= 32) { LAUNCH(4); }
     else { LAUNCH(8); }
 #undef LAUNCH
     return ti_check_launch("gemm_skinny");
+}
+
+extern "C" int ti_gemm_skinny(const void* a, const void* w, float* c, void* out_act, int m, int n,
+                              int k, int lda, int ldw, int ldc, int ld_act, int mode, void* stream) {
+    TI_REQUIRE(mode >= MODE_STORE && mode <= MODE_SWIGLU, "gemm_skinny: mode %d", mode);
+    return skinny(a, w, c, out_act, m, n, k, lda, ldw, ldc, ld_act, mode, 0.0f, 0.0f, stream);
+}
+
+// out_act[m, n] (bfloat16) = xielu(a w^T): act_p z^2 + z/2 for z > 0, act_q (exp(z) - 1 - z) + z/2 otherwise
+extern "C" int ti_gemm_skinny_xielu(const void* a, const void* w, void* out_act, int m, int n, int k, int lda,
+                                    int ldw, int ld_act, float act_p, float act_q, void* stream) {
+    return skinny(a, w, nullptr, out_act, m, n, k, lda, ldw, 0, ld_act, MODE_XIELU, act_p, act_q, stream);
 }

@@ -41,86 +41,129 @@ token_shift_mix_kernel(const TH* h, const float* __restrict__ mu, int n_mix, int
     }
 }
 
-// Tokens are staged a tile (16 or 8) at a time: all threads fetch the tile's r, k, v, g and decays into shared
-// memory (the next tile's values are already in registers while this one is worked on), then the
-// tile's tokens follow one another without a barrier: column j of the state belongs to four
-// neighbouring lanes, lane part s holding its rows s, s + 4, s + 8, ...; the four partial sums of
-// o_j meet through two shuffles.  The unit norm of the tile's rows is taken afterwards, a warp per
-// token.
-constexpr int WKV_IS = 4;
+// Tokens are staged a tile (16 or 8) at a time: cp.async brings the tile's r, k, v, g and decay arguments
+// into one of two buffers in shared memory while the tile before is worked on, then
+// the tile's tokens follow one another without a barrier: column j of the state belongs to four
+// neighbouring lanes, each holding a quarter of its rows (read four at a time); the four partial sums
+// of o_j meet through two shuffles.  The unit norm of the tile's rows is taken afterwards, a warp per
+// token.  JS > 1 (long portions of few requests): a head's columns are cut over JS blocks, each with
+// the whole of r, k and the decays and its own columns of v; the blocks write o as float32 and a
+// second launch (wkv_finish) takes the norm, the weight and the gate.
+// lanes per state column: four, or, where a head's columns are cut over blocks (long portions), up to
+// sixteen, so that a token's chain of multiply-adds is a quarter as long
+constexpr int wkv_lanes(int dmax, int js) { return js == 1 ? 4 : (dmax / 4 < 16 ? dmax / 4 : 16); }
 
-template <typename TH, typename TO, int DMAX>
-__global__ void __launch_bounds__(DMAX * WKV_IS)
+__device__ __forceinline__ void cp_async4(float* dst, const float* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 4 : 0;                     // nothing is read and zero is written otherwise
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+
+template <typename TH, typename TO, int DMAX, int JS>
+__global__ void __launch_bounds__(DMAX / JS * wkv_lanes(DMAX, JS))
 wkv_recurrence_kernel(const float* r, const float* k, const float* v, const float* g, const float* a,
                       int in_stride, const float* __restrict__ w0, const float* __restrict__ u,
                       const float* __restrict__ norm_weight, float eps, const TH* h, int width,
                       const int* __restrict__ cu_q, const int* __restrict__ slots, float* state,
                       size_t state_stride, size_t prev_offset, int num_heads, int d,
-                      TO* __restrict__ out) {
-    constexpr int WKV_TT = DMAX > 64 ? 8 : 16;           // tokens per staged tile (48 KB of shared memory at most)
+                      TO* __restrict__ out, float* __restrict__ o_raw) {
+    constexpr int WKV_TT = (DMAX > 64 ? 8 : 16) / (JS == 1 ? 2 : 1);   // tokens per staged tile (48 KB of shared memory at most)
+    constexpr int WKV_IS = wkv_lanes(DMAX, JS);
     constexpr int NI = DMAX / WKV_IS;                    // state rows per thread
-    constexpr int THREADS = DMAX * WKV_IS;
-    constexpr int PER = WKV_TT * DMAX / THREADS;         // staged elements of one array per thread
-    __shared__ __align__(16) float rs[WKV_TT][DMAX], ks[WKV_TT][DMAX], ws[WKV_TT][DMAX];
-    __shared__ float vs[WKV_TT][DMAX], gs[WKV_TT][DMAX], os[WKV_TT][DMAX], us[DMAX], inv_s[WKV_TT];
+    constexpr int DC = DMAX / JS;                        // state columns of this block
+    constexpr int THREADS = DC * WKV_IS;
+    constexpr int PER = WKV_TT * DMAX / THREADS;         // staged elements of r, k, decay per thread
+    constexpr int PERC = (WKV_TT * DC + THREADS - 1) / THREADS;   // ... of v and g (this block's columns)
+    // two buffers of a tile's inputs: one is read while cp.async fills the other
+    __shared__ __align__(16) float rs[2][WKV_TT][DMAX], ks[2][WKV_TT][DMAX], as[2][WKV_TT][DMAX], ws[WKV_TT][DMAX];
+    __shared__ float vs[2][WKV_TT][DC], gs[2][WKV_TT][DC], os[WKV_TT][DC], inv_s[WKV_TT];
     const int req = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
-    const int j = tid / WKV_IS, part = tid % WKV_IS;
+    const int c0 = blockIdx.z * DC;                      // first column of this block
+    const int j = c0 + tid / WKV_IS, part = tid % WKV_IS;
     const int t0 = cu_q[req], t1 = cu_q[req + 1];
     const bool live = j < d;
     float* slot = state + (size_t)slots[req] * state_stride;
     float* s_head = slot + (size_t)head * d * d;
-    float S[NI];
+    // lane part `part` has rows 4 IS q + 4 part + x (x = 0..3, q = 0..NI/4 - 1) of column j and their
+    // bonus u: the lanes of a column read contiguous bytes of a token's r, k or decay, four rows each
+    float S[NI], ur[NI];
 #pragma unroll
     for (int ii = 0; ii < NI; ++ii) {
-        const int i = part + WKV_IS * ii;
+        const int i = (ii / 4) * (4 * WKV_IS) + part * 4 + ii % 4;
         S[ii] = (live && i < d) ? s_head[(size_t)i * d + j] : 0.0f;
+        ur[ii] = i < d ? u[head * d + i] : 0.0f;
     }
-    if (tid < DMAX) us[tid] = tid < d ? u[head * d + tid] : 0.0f;
 
-    float fr[PER], fk[PER], fa[PER], fv[PER], fg[PER];
-    auto fetch = [&](int tile0) {                        // the tile's values into registers
+    auto fetch = [&](int tile0, int buf) {               // the tile's inputs on their way into buffer `buf`
 #pragma unroll
         for (int x = 0; x < PER; ++x) {
             const int e = tid + x * THREADS, tt = e / DMAX, c = e % DMAX;
             const bool ok = tile0 + tt < t1 && c < d;
-            const size_t at = (size_t)(tile0 + tt) * in_stride + head * d + c;
-            fr[x] = ok ? r[at] : 0.0f;
-            fk[x] = ok ? k[at] : 0.0f;
-            fa[x] = ok ? a[at] + w0[head * d + c] : 0.0f;
-            fv[x] = ok ? v[at] : 0.0f;
-            fg[x] = ok ? g[at] : 0.0f;
+            const size_t at = ok ? (size_t)(tile0 + tt) * in_stride + head * d + c : 0;
+            cp_async4(&rs[buf][tt][c], r + at, ok);
+            cp_async4(&ks[buf][tt][c], k + at, ok);
+            cp_async4(&as[buf][tt][c], a + at, ok);
         }
+#pragma unroll
+        for (int x = 0; x < PERC; ++x) {
+            const int e = tid + x * THREADS, tt = e / DC, c = c0 + e % DC;
+            if (e >= WKV_TT * DC) break;
+            const bool ok = tile0 + tt < t1 && c < d;
+            const size_t at = ok ? (size_t)(tile0 + tt) * in_stride + head * d + c : 0;
+            cp_async4(&vs[buf][tt][e % DC], v + at, ok);
+            if (JS == 1) cp_async4(&gs[buf][tt][e % DC], g + at, ok);
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
     };
-    if (t0 < t1) fetch(t0);
-    for (int tile0 = t0; tile0 < t1; tile0 += WKV_TT) {
-        __syncthreads();                                 // the tile before has been read and written out
+    if (t0 < t1) fetch(t0, 0);
+    int buf = 0;
+    for (int tile0 = t0; tile0 < t1; tile0 += WKV_TT, buf ^= 1) {
+        // the buffer that is filled next was read two tiles ago; everyone has left that tile
+        if (tile0 + WKV_TT < t1) {
+            fetch(tile0 + WKV_TT, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncthreads();                                 // this tile's inputs are here; the tile before is written out
 #pragma unroll
         for (int x = 0; x < PER; ++x) {
             const int e = tid + x * THREADS, tt = e / DMAX, c = e % DMAX;
-            rs[tt][c] = fr[x];
-            ks[tt][c] = fk[x];
-            ws[tt][c] = expf(-expf(fa[x]));
-            vs[tt][c] = fv[x];
-            gs[tt][c] = fg[x];
+            ws[tt][c] = c < d ? expf(-expf(as[buf][tt][c] + w0[head * d + c])) : 0.0f;
         }
         __syncthreads();
-        if (tile0 + WKV_TT < t1) fetch(tile0 + WKV_TT);  // in flight while this tile is worked on
         const int nt = min(WKV_TT, t1 - tile0);
         for (int tt = 0; tt < nt; ++tt) {
-            const float vj = vs[tt][j];
+            const float vj = vs[buf][tt][j - c0];
             float o = 0.0f;
+            const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][part * 4]);
+            const float4* r4 = reinterpret_cast<const float4*>(&rs[buf][tt][part * 4]);
+            const float4* w4 = reinterpret_cast<const float4*>(&ws[tt][part * 4]);
 #pragma unroll
-            for (int ii = 0; ii < NI; ++ii) {
-                const int i = part + WKV_IS * ii;
-                const float kv = ks[tt][i] * vj;
-                o = fmaf(rs[tt][i], fmaf(us[i], kv, S[ii]), o);
-                S[ii] = fmaf(ws[tt][i], S[ii], kv);
+            for (int q4 = 0; q4 < NI / 4; ++q4) {        // four rows a load
+                const float4 kq = k4[q4 * WKV_IS], rq = r4[q4 * WKV_IS], wq = w4[q4 * WKV_IS];
+                const float kk[4] = {kq.x, kq.y, kq.z, kq.w}, rr[4] = {rq.x, rq.y, rq.z, rq.w};
+                const float ww[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const int ii = q4 * 4 + x;
+                    const float kv = kk[x] * vj;
+                    o = fmaf(rr[x], fmaf(ur[ii], kv, S[ii]), o);
+                    S[ii] = fmaf(ww[x], S[ii], kv);
+                }
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (part == 0) os[tt][j] = live ? o : 0.0f;
+#pragma unroll
+            for (int sh = 1; sh < WKV_IS; sh *= 2) o += __shfl_xor_sync(0xffffffffu, o, sh);
+            if (part == 0) os[tt][j - c0] = live ? o : 0.0f;
         }
         __syncthreads();
+        if (JS > 1) {                                    // the row's other columns are elsewhere
+            for (int e = tid; e < nt * DC; e += THREADS) {
+                const int tt = e / DC, c = c0 + e % DC;
+                if (c < d) o_raw[(size_t)(tile0 + tt) * num_heads * d + head * d + c] = os[tt][e % DC];
+            }
+            continue;
+        }
         for (int tt = tid / 32; tt < nt; tt += THREADS / 32) {       // a warp per token: its unit norm
             float ss = 0.0f;
             for (int c = tid % 32; c < d; c += 32) ss = fmaf(os[tt][c], os[tt][c], ss);
@@ -128,10 +171,10 @@ wkv_recurrence_kernel(const float* r, const float* k, const float* v, const floa
             if (tid % 32 == 0) inv_s[tt] = 1.0f / sqrtf(ss / (float)d + eps);
         }
         __syncthreads();
-        for (int e = tid; e < nt * DMAX; e += THREADS) {
-            const int tt = e / DMAX, c = e % DMAX;
+        for (int e = tid; e < nt * DC; e += THREADS) {
+            const int tt = e / DC, c = e % DC;
             if (c < d) {
-                const float gj = gs[tt][c];
+                const float gj = gs[buf][tt][c];
                 const float y = os[tt][c] * inv_s[tt] * norm_weight[head * d + c] * (gj / (1.0f + expf(-gj)));
                 out[(size_t)(tile0 + tt) * num_heads * d + head * d + c] = from_f32<TO>(y);
             }
@@ -141,14 +184,33 @@ wkv_recurrence_kernel(const float* r, const float* k, const float* v, const floa
         if (live) {
 #pragma unroll
             for (int ii = 0; ii < NI; ++ii) {
-                const int i = part + WKV_IS * ii;
+                const int i = (ii / 4) * (4 * WKV_IS) + part * 4 + ii % 4;
                 if (i < d) s_head[(size_t)i * d + j] = S[ii];
             }
         }
-        if (head == 0) {
+        if (head == 0 && blockIdx.z == 0) {
             const TH* last = h + (size_t)(t1 - 1) * width;
             for (int e = tid; e < width; e += THREADS) slot[prev_offset + e] = to_f32(last[e]);
         }
+    }
+}
+
+// out[t, head] = o / rms(o) * weight * silu(g) for the rows that column-split blocks left as float32:
+// a warp per (token, head)
+template <typename TO>
+__global__ void __launch_bounds__(256)
+wkv_finish_kernel(const float* o_raw, const float* g, int g_stride, const float* __restrict__ norm_weight, float eps,
+                  int num_items, int num_heads, int d, TO* __restrict__ out) {
+    const int item = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= num_items) return;
+    const int t = item / num_heads, head = item % num_heads;
+    const float* o = o_raw + (size_t)item * d;
+    float ss = 0.0f;
+    for (int c = lane; c < d; c += 32) ss = fmaf(o[c], o[c], ss);
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
+    for (int c = lane; c < d; c += 32) {
+        const float gj = g[(size_t)t * g_stride + head * d + c];
+        out[(size_t)item * d + c] = from_f32<TO>(o[c] * inv * norm_weight[head * d + c] * (gj / (1.0f + expf(-gj))));
     }
 }
 
@@ -188,21 +250,33 @@ extern "C" int ti_token_shift_mix(const void* h, int h_dtype, const float* mu, i
 
 extern "C" int ti_wkv_recurrence_max_dim() { return 128; }
 
+// col_split: 1, or 4 to cut a head's state columns over four blocks (o_raw: float32 [T, heads * d] scratch)
 extern "C" int ti_wkv_recurrence(const float* r, const float* k, const float* v, const float* g, const float* a,
                                  int in_stride, const float* w0, const float* u, const float* norm_weight,
                                  float eps, const void* h, int h_dtype, int width, const int* cu_q,
                                  const int* slots, float* state, long long state_stride, long long prev_offset,
-                                 int num_requests, int num_heads, int d, void* out, void* stream) {
+                                 int num_requests, int num_tokens, int num_heads, int d, int col_split,
+                                 float* o_raw, void* out, void* stream) {
     if (num_requests == 0) return 0;
     TI_REQUIRE(d >= 1 && d <= 128, "wkv_recurrence: head size %d must be at most 128", d);
-    dim3 grid(num_requests, num_heads);
+    TI_REQUIRE(col_split == 1 || (col_split == 4 && o_raw != nullptr), "wkv_recurrence: columns are cut over 1 or 4 "
+               "blocks, and four need scratch");
+    dim3 grid(num_requests, num_heads, col_split);
     cudaStream_t s = (cudaStream_t)stream;
-#define LAUNCH(TH, DMAX)                                                                           \
-    wkv_recurrence_kernel<TH, TH, DMAX><<<grid, DMAX * WKV_IS, 0, s>>>(                                       \
+#define LAUNCH(TH, DMAX, JS)                                                                       \
+    wkv_recurrence_kernel<TH, TH, DMAX, JS><<<grid, DMAX / JS * wkv_lanes(DMAX, JS), 0, s>>>(                      \
         r, k, v, g, a, in_stride, w0, u, norm_weight, eps, (const TH*)h, width, cu_q, slots, state,    \
-        (size_t)state_stride, (size_t)prev_offset, num_heads, d, (TH*)out)
+        (size_t)state_stride, (size_t)prev_offset, num_heads, d, (TH*)out, o_raw)
 #define CALL(TH)                                                                                   \
-    if (d <= 32) LAUNCH(TH, 32); else if (d <= 64) LAUNCH(TH, 64); else LAUNCH(TH, 128)
+    if (col_split == 4) {                                                                          \
+        if (d <= 32) LAUNCH(TH, 32, 4); else if (d <= 64) LAUNCH(TH, 64, 4); else LAUNCH(TH, 128, 4); \
+        if (int rc = ti_check_launch("wkv_recurrence")) return rc;                                 \
+        const int items = num_tokens * num_heads;                                                  \
+        wkv_finish_kernel<TH><<<(items + 7) / 8, 256, 0, s>>>(o_raw, g, in_stride, norm_weight, eps, items, \
+                                                            num_heads, d, (TH*)out);               \
+        return ti_check_launch("wkv_finish");                                                      \
+    }                                                                                              \
+    if (d <= 32) LAUNCH(TH, 32, 1); else if (d <= 64) LAUNCH(TH, 64, 1); else LAUNCH(TH, 128, 1)
     if (h_dtype == TI_F32) { CALL(float); }
     else if (h_dtype == TI_BF16) { CALL(bf16); }
     else return ti_fail("wkv_recurrence: dtype code %d is not supported", h_dtype);

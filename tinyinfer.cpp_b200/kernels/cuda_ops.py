@@ -12,6 +12,7 @@ pack_gate_up(gate, up) -> w'                 the stacked gate/up weight
 embed(table, token_ids, out)                 out[t] = float32(table[token_ids[t]])
 rmsnorm(x, weight, eps, out, rows=None)      out[r] = norm(x[rows[r]] or x[r]), rounded to out.dtype
 linear(a, w, out, accumulate=False)          out (+)= a @ w.T in float32
+linear_xielu(h, w, ap, aq, out)              out = xielu(h @ w.T), one launch for few rows
 gate_up_swiglu(h, w, out)                    out = silu(h @ gate.T) * (h @ up.T)
 qk_norm_rope_store(qkv, ..., rotation, ...)  q/k head norm, rotation, k/v into pages, q out
 qkv_rope_store(h, w, ..., rotation, ...)     the QKV product followed by qk_norm_rope_store, in one
@@ -223,6 +224,7 @@ class CudaOps(MixerOps):
             b.ti_last_error.restype = ctypes.c_char_p
             b.ti_gemm_skinny.argtypes = [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]
             b.ti_gemm_skinny_supported.argtypes = [_i, _i, _i, _i, _i]
+            b.ti_gemm_skinny_xielu.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp]
             b.ti_ffn_decode_supported.argtypes = [_i] * 8
             b.ti_ffn_decode.argtypes = [_vp, _vp, _vp, _vp, _vp] + [_i] * 8 + [_vp, _vp, _vp]
             b.ti_attn_out_ffn_decode_supported.argtypes = [_i] * 10
@@ -534,6 +536,25 @@ class CudaOps(MixerOps):
         self.linear(h, w_gate_up, gu)
         self._ok(self.core.ti_swiglu(gu.data_ptr(), m, inter, int(interleaved), out.data_ptr(),
                                      _code(out, "swiglu"), self._stream()))
+
+    def linear_xielu(self, h, w, ap, aq, out):
+        """out = xielu(h @ w.T) in the activation dtype: ``ap z^2 + z/2`` where ``z > 0``, ``aq (exp(z) -
+        1 - z) + z/2`` elsewhere.  Few rows run as one launch (the product's epilogue applies the
+        activation); otherwise the product is followed by ``xielu_rows``."""
+        m, k = h.shape
+        n = w.shape[0]
+        _need(w.shape[1] == k and tuple(out.shape) == (m, n) and out.dtype == h.dtype
+              and h.stride(1) == w.stride(1) == out.stride(1) == 1, "linear_xielu: shapes do not agree")
+        if (h.dtype == w.dtype == torch.bfloat16 and h.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+                and (self.few_tc_min_bytes is None or n * k * 2 <= self.few_tc_min_bytes)
+                and self.bf16.ti_gemm_skinny_supported(m, n, k, h.stride(0), w.stride(0))):
+            self._ok(self.bf16.ti_gemm_skinny_xielu(h.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, h.stride(0),
+                                                    w.stride(0), out.stride(0), float(ap), float(aq), self._stream()),
+                     self.bf16)
+            return
+        z = torch.empty((m, n), dtype=torch.float32, device=h.device)
+        self.linear(h, w, z)
+        self.xielu_rows(z, ap, aq, out)
 
     def swiglu_ffn(self, h, w_gate_up, w_down, residual, may_defer=False):
         """residual += (silu(h Wgate^T) * (h Wup^T)) Wdown^T, with ``w_gate_up`` from pack_gate_up.

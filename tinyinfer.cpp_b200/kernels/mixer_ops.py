@@ -83,7 +83,7 @@ class MixerOps:
                                                _i, _i, _i, _f, _f, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp]
             b.ti_token_shift_mix.argtypes = [_vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _ll, _ll, _vp, _vp]
             b.ti_wkv_recurrence.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _f, _vp, _i, _i, _vp, _vp,
-                                            _vp, _ll, _ll, _i, _i, _i, _vp, _vp]
+                                            _vp, _ll, _ll, _i, _i, _i, _i, _i, _vp, _vp, _vp]
             b.ti_tanh_rows.argtypes = [_vp, _ll, _vp, _i, _vp]
             b.ti_xielu_rows.argtypes = [_vp, _ll, _f, _f, _vp, _i, _vp]
             self._mixers = b
@@ -283,11 +283,18 @@ class MixerOps:
         self._must(h.is_contiguous() and out.is_contiguous() and out.dtype == h.dtype and tuple(out.shape) == (t, n),
                    "wkv_recurrence: out must be [T, heads * d] in the activation dtype")
         self._must(bool(state.writes), "wkv_recurrence writes its state")
+        # long portions of few requests leave most SMs without a head: a head's state columns are then
+        # cut over four blocks, and a second launch takes the norm and the gate (a rule of the step's
+        # shape alone)
+        split = 4 if (step.max_q_len >= 64 and step.num_requests * num_heads * 2 <= self.num_sms) else 1
+        o_raw = torch.empty((t, n), dtype=torch.float32, device=h.device) if split > 1 else None
+        if split > 1:
+            self.launches += 1
         self._mx(self.mixers.ti_wkv_recurrence(
             r.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), a.data_ptr(), r.stride(0), w0.data_ptr(),
             u.data_ptr(), norm_weight.data_ptr(), float(eps), h.data_ptr(), _CODE[h.dtype], h.shape[1],
             step.cu_q.data_ptr(), state.slots.data_ptr(), st.data_ptr(), st[0].numel(), int(prev_offset),
-            step.num_requests, num_heads, d, out.data_ptr(), self._stream()))
+            step.num_requests, t, num_heads, d, split, _ptr(o_raw), out.data_ptr(), self._stream()))
 
     # ---- activations ---------------------------------------------------------------------------
     def tanh_rows(self, x, out):

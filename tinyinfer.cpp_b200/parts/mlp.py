@@ -71,10 +71,8 @@ class XieluMlp(Part):
         self.ap, self.aq = _softplus(p), 0.5 + _softplus(q)
 
     def forward(self, ops, h, residual, step):
-        z = torch.empty((h.shape[0], self.intermediate_size), dtype=torch.float32, device=h.device)
-        ops.linear(h, self.w_up, z)
-        y = torch.empty(z.shape, dtype=h.dtype, device=h.device)
-        ops.xielu_rows(z, self.ap, self.aq, y)
+        y = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
+        ops.linear_xielu(h, self.w_up, self.ap, self.aq, y)
         ops.linear(y, self.w_down, residual, accumulate=True, may_defer=True)
 
 
