@@ -143,14 +143,116 @@ latent_prepare_kernel(const float* proj, int stride, const float* __restrict__ l
         dst[rank + e] = from_f32<TC>(turned(lat + rank, e, pos, inv_freq, 1.0f));
 }
 
-// out[t, h, n] = sum_k in[t, h, k] * w[h, k, n]; a block has 16 tokens of one head and 128 columns;
-// the tokens' inputs lie in shared memory with the tokens of one k side by side, so that a thread
-// reads them four at a time, the same address for the whole warp
+// out[t, h, n] = sum_k in[t, h, k] * w[h, k, n]; a block has 16 tokens of one head and 128 columns.
+// Its eight warps take an eighth of k each, a lane four neighbouring columns (8 bytes of a weight row
+// a load, eight loads in flight), so that a step of few tokens, whose grid is a block or a few per
+// head, still has the weights of a head on their way at once; the tokens' inputs lie in shared
+// memory with the tokens of one k side by side (read four at a time, the same address for the whole
+// warp), and the warps' partial sums meet in shared memory in a fixed order.
 constexpr int HP_TOKENS = 16;
+constexpr int HP_WARPS = 8;
+
+template <typename TW> __device__ __forceinline__ void load4(const TW* p, bool whole, int left, float (&w)[4]);
+template <> __device__ __forceinline__ void load4<bf16>(const bf16* p, bool whole, int left, float (&w)[4]) {
+    if (whole) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        w[0] = __bfloat162float(lo.x); w[1] = __bfloat162float(lo.y);
+        w[2] = __bfloat162float(hi.x); w[3] = __bfloat162float(hi.y);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = i < left ? __bfloat162float(p[i]) : 0.0f;
+    }
+}
+template <> __device__ __forceinline__ void load4<float>(const float* p, bool whole, int left, float (&w)[4]) {
+    if (whole) {
+        const float4 raw = *reinterpret_cast<const float4*>(p);
+        w[0] = raw.x; w[1] = raw.y; w[2] = raw.z; w[3] = raw.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = i < left ? p[i] : 0.0f;
+    }
+}
+
+template <typename TI, typename TW, typename TO>
+__global__ void __launch_bounds__(HP_WARPS * 32)
+head_project_kernel(const TI* in, int in_stride_t, int in_stride_h, const TW* __restrict__ w, int n_in,
+                    int n_out, TO* out, int out_stride_t, int out_stride_h, int num_tokens, int vec_ok) {
+    extern __shared__ __align__(16) float xs[];      // [n_in][HP_TOKENS]; afterwards the warps' partial sums
+    const int t0 = blockIdx.x * HP_TOKENS, h = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.z * 128 + lane * 4;      // this lane's first column
+    const int nt = min(HP_TOKENS, num_tokens - t0);
+    for (int e = threadIdx.x; e < HP_TOKENS * n_in; e += HP_WARPS * 32) {
+        const int tt = e / n_in, k = e % n_in;
+        xs[k * HP_TOKENS + tt] =
+            tt < nt ? to_f32(in[(size_t)(t0 + tt) * in_stride_t + (size_t)h * in_stride_h + k]) : 0.0f;
+    }
+    __syncthreads();
+    float acc[HP_TOKENS][4];
+#pragma unroll
+    for (int i = 0; i < HP_TOKENS; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+    const int left = n_out - n0;                     // columns of this lane that exist
+    if (left > 0) {
+        const bool whole = vec_ok && left >= 4;
+        const TW* wh = w + (size_t)h * n_in * n_out + n0;
+        const int per = (n_in + HP_WARPS - 1) / HP_WARPS;
+        const int k_end = min(n_in, (warp + 1) * per);
+#pragma unroll 8
+        for (int k = warp * per; k < k_end; ++k) {
+            float wv[4];
+            load4<TW>(wh + (size_t)k * n_out, whole, left, wv);
+            const float4* x4 = reinterpret_cast<const float4*>(xs + k * HP_TOKENS);
+#pragma unroll
+            for (int i = 0; i < HP_TOKENS / 4; ++i) {
+                const float4 x = x4[i];
+                const float xv[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[4 * i + a][c] = fmaf(xv[a], wv[c], acc[4 * i + a][c]);
+            }
+        }
+    }
+    // the warps' sums meet in a fixed order (the upper half of the warps hands its sums to the lower
+    // half, three times), so a row's bits are the same in every run
+    float4* meet = reinterpret_cast<float4*>(xs);    // [warp][HP_TOKENS][32 lanes] of four columns
+#pragma unroll
+    for (int half = HP_WARPS / 2; half >= 1; half /= 2) {
+        __syncthreads();                             // the inputs, or the round before, have been read
+        if (warp >= half && warp < 2 * half) {
+#pragma unroll
+            for (int i = 0; i < HP_TOKENS; ++i)
+                meet[((warp - half) * HP_TOKENS + i) * 32 + lane] = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        }
+        __syncthreads();
+        if (warp < half) {
+#pragma unroll
+            for (int i = 0; i < HP_TOKENS; ++i) {
+                const float4 o = meet[(warp * HP_TOKENS + i) * 32 + lane];
+                acc[i][0] += o.x; acc[i][1] += o.y; acc[i][2] += o.z; acc[i][3] += o.w;
+            }
+        }
+    }
+    if (warp == 0 && left > 0) {
+#pragma unroll
+        for (int i = 0; i < HP_TOKENS; ++i) {
+            if (i >= nt) break;
+            TO* dst = out + (size_t)(t0 + i) * out_stride_t + (size_t)h * out_stride_h + n0;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                if (c < left) dst[c] = from_f32<TO>(acc[i][c]);
+        }
+    }
+}
+
+// The same product for many tokens, where the grid has blocks enough: four warps, a thread per column,
+// all of k in one thread (no meeting of partial sums).
 template <typename TI, typename TW, typename TO>
 __global__ void __launch_bounds__(128)
-head_project_kernel(const TI* in, int in_stride_t, int in_stride_h, const TW* __restrict__ w, int n_in,
-                    int n_out, TO* out, int out_stride_t, int out_stride_h, int num_tokens) {
+head_project_rows_kernel(const TI* in, int in_stride_t, int in_stride_h, const TW* __restrict__ w, int n_in,
+                         int n_out, TO* out, int out_stride_t, int out_stride_h, int num_tokens) {
     extern __shared__ __align__(16) float xs[];      // [n_in][HP_TOKENS]
     const int t0 = blockIdx.x * HP_TOKENS, h = blockIdx.y;
     const int n = blockIdx.z * 128 + threadIdx.x;
@@ -335,14 +437,28 @@ extern "C" int ti_head_project(const void* in, int in_dtype, int in_stride_t, in
                                int out_stride_h, int num_tokens, int num_heads, void* stream) {
     if (num_tokens == 0 || num_heads == 0) return 0;
     TI_REQUIRE(in_dtype == out_dtype, "head_project: input and output must have one dtype");
-    const size_t smem = (size_t)HP_TOKENS * n_in * sizeof(float);
+    size_t smem = (size_t)HP_TOKENS * n_in * sizeof(float);
+    const size_t meet = (size_t)(HP_WARPS / 2) * HP_TOKENS * 128 * sizeof(float);     // where the warps' sums meet
+    if (smem < meet) smem = meet;
     TI_REQUIRE(smem <= 48 * 1024, "head_project: %d inputs per head are more than the kernel stages", n_in);
     dim3 grid((num_tokens + HP_TOKENS - 1) / HP_TOKENS, num_heads, (n_out + 127) / 128);
+    // four columns a load where every group of four starts on a multiple of the load's size
+    const int vec_ok = n_out % 4 == 0 && (uintptr_t)w % 16 == 0;
     cudaStream_t s = (cudaStream_t)stream;
+    // few blocks (a step of single tokens): the form whose warps split k, so that a head's weights are
+    // on their way at once; many blocks: a thread per column with all of k.  (A row's bits can differ
+    // between the two forms; within a form they depend on the row alone.)
+    // Float32 rows always take the second form: their bits must not depend on the step around them.
+    const bool few = in_dtype != TI_F32 && (long long)grid.x * grid.y * grid.z <= 512;
 #define CALL(TI_, TW_)                                                                            \
-    head_project_kernel<TI_, TW_, TI_><<<grid, 128, smem, s>>>(                                    \
-        (const TI_*)in, in_stride_t, in_stride_h, (const TW_*)w, n_in, n_out, (TI_*)out,            \
-        out_stride_t, out_stride_h, num_tokens)
+    if (few)                                                                                      \
+        head_project_kernel<TI_, TW_, TI_><<<grid, HP_WARPS * 32, smem, s>>>(                      \
+            (const TI_*)in, in_stride_t, in_stride_h, (const TW_*)w, n_in, n_out, (TI_*)out,        \
+            out_stride_t, out_stride_h, num_tokens, vec_ok);                                       \
+    else                                                                                          \
+        head_project_rows_kernel<TI_, TW_, TI_><<<grid, 128, smem, s>>>(                           \
+            (const TI_*)in, in_stride_t, in_stride_h, (const TW_*)w, n_in, n_out, (TI_*)out,        \
+            out_stride_t, out_stride_h, num_tokens)
     if (in_dtype == TI_F32 && w_dtype == TI_F32) { CALL(float, float); }
     else if (in_dtype == TI_F32 && w_dtype == TI_BF16) { CALL(float, bf16); }
     else if (in_dtype == TI_BF16 && w_dtype == TI_BF16) { CALL(bf16, bf16); }
