@@ -271,6 +271,27 @@ def test_sink_and_shared_rows(ops, dtype):
     assert out.view(t, heads, dv)[:, 0].abs().max() < 1e-6          # the sink of 60 took everything
 
 
+@pytest.mark.parametrize("heads", [16, 24, 40])
+def test_shared_rows_of_single_tokens_with_many_heads(ops, heads):
+    """Single tokens over shared rows wide enough for several slices of value columns, with as many
+    heads as one block takes and more."""
+    dk, dv, ps = 288, 256, 16
+    ctx = [70, 9, 300]
+    step, cache, bt, positions, req = _paged(ctx, [1, 1, 1], ps, dk, torch.bfloat16, seed=heads)
+    g = torch.Generator().manual_seed(heads)
+    rows = [torch.randn((c, 1, dk), generator=g) * 0.5 for c in ctx]
+    _fill(cache, bt, rows, rows, 1, dk, 0)
+    q = torch.randn((3, heads, dk), generator=g) * 0.3
+    sink = torch.randn((heads,), generator=g)
+    out = torch.empty((3, heads * dv), dtype=torch.bfloat16, device=DEV)
+    ops.attention_options(q.reshape(3, -1).bfloat16().to(DEV), step, cache, out, heads, 1, dk, dv, 0.1,
+                          sink=sink.to(DEV), shared_rows=True)
+    rd = lambda x: x.bfloat16().double()
+    for r in range(3):
+        want = plain.attend(rd(q[r:r + 1]), rd(rows[r]), rd(rows[r])[:, :, :dv], [ctx[r] - 1], 0.1, sink=sink.double())
+        assert (out[r].cpu().double().view(1, heads, dv) - want).abs().max() < 2e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sizes", [(3, 8, 20, 11), (1, 16, 16, 1), (4, 64, 96, 70), (2, 130, 12, 9)])
 def test_head_project(ops, sizes, dtype):

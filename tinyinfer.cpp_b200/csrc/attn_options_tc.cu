@@ -375,6 +375,7 @@ attn_options_tc_kernel(const bf16* q, const int* __restrict__ tiles, const int* 
         }
         return;
     }
+    if (MODE == 2 && slice >= dv / DVS) return;      // a warp without a slice of its own has nothing to write
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int h = row_h[r];
@@ -472,7 +473,8 @@ extern "C" int ti_attn_options_tc_group_rows(int num_heads, int num_kv_heads) {
 // 64 / group_rows consecutive tokens of one request.  part_o/part_ml: float32 scratch of
 // [tokens, heads, nsplit, dv] and [tokens, heads, nsplit, 2] when nsplit > 1.  key_split: every tile has at
 // most 16 rows (tokens x group_rows), and the warps of a block share them and split a tile's keys (1) or,
-// with shared rows, the slices of the value columns (2).
+// with shared rows, the slices of the value columns (2; every tile is then a single token, and a group of more
+// than 16 heads is spread over blocks of 16).
 extern "C" int ti_attn_options_tc(const void* q, const int* tiles, int num_tiles, int num_tokens,
                                   const int* positions, const int* block_table, int bt_stride, const void* pages,
                                   int num_pages, int page_size, int num_heads, int num_kv_heads, int dk, int dv,
@@ -487,9 +489,10 @@ extern "C" int ti_attn_options_tc(const void* q, const int* tiles, int num_tiles
                "(a multiple of 16) are not supported", dk, dv, page_size);
     TI_REQUIRE(nsplit >= 1 && nsplit <= 64 && (nsplit == 1 || (part_o && part_ml)), "attn_options_tc: runs and scratch");
     TI_REQUIRE(num_tiles <= 65535, "attn_options_tc: %d tiles exceed the grid limit", num_tiles);
-    TI_REQUIRE(!key_split || ti_attn_options_tc_group_rows(num_heads, num_kv_heads) <= 16,
+    TI_REQUIRE(key_split != 1 || ti_attn_options_tc_group_rows(num_heads, num_kv_heads) <= 16,
                "attn_options_tc: warps split the keys only when a tile has at most 16 rows");
-    const int gp = ti_attn_options_tc_group_rows(num_heads, num_kv_heads);
+    int gp = ti_attn_options_tc_group_rows(num_heads, num_kv_heads);
+    if (key_split == 2 && gp > 16) gp = 16;      // a tile is one token: more heads than 16 take several blocks
     const int group = num_heads / num_kv_heads, head_blocks = (group + gp - 1) / gp;
     const int dvs = value_slice(dv);
     const size_t smem = smem_bytes(dk, dv, shared_rows);

@@ -214,8 +214,9 @@ class MixerOps:
             single = getattr(step, "max_q_len", 0) == 1
             # single tokens of few heads: the warps of a block share the rows and split the keys (1) or,
             # over shared rows, the slices of the value columns (2)
-            mode = 0 if not (single and gp <= 16) else 2 if (shared_rows and 1 < slices <= 4) else 1
-            blocks = tiles.shape[0] * num_kv_heads * -(-(num_heads // num_kv_heads) // gp) * (1 if mode == 2 else slices)
+            mode = 0 if not single else 2 if (shared_rows and 1 < slices <= 4) else 1 if gp <= 16 else 0
+            head_blocks = -(-(num_heads // num_kv_heads) // (min(gp, 16) if mode == 2 else gp))
+            blocks = tiles.shape[0] * num_kv_heads * head_blocks * (1 if mode == 2 else slices)
             if single and blocks < 2 * self.num_sms:
                 most = step.max_position or step.max_ctx_len
                 for bound in (window, chunk):
