@@ -100,7 +100,8 @@ def chunked_attention(h, w, p, m, eps, first_position=0, past=None):
     if past is not None:
         k, v = torch.cat([past[0], k]), torch.cat([past[1], v])
     gate = torch.sigmoid(h @ w[p + "g"].T)                        # [T, H]
-    out = attend(q, k, v, pos, m["scale"], m["mask"]["size"], m["softcap"], w[p + "temp"]) * gate[:, :, None]
+    chunk = m["mask"]["size"] if m.get("mask") else None
+    out = attend(q, k, v, pos, m["scale"], chunk, m.get("softcap"), w[p + "temp"]) * gate[:, :, None]
     return out.reshape(t, nh * dv) @ w[p + "o"].T, (k, v)
 
 

@@ -34,7 +34,8 @@ def test_registry_names_the_design():
     (("layers", 3, "weights_of"), 3, "another layer"),
     (("layers", 3, "weights_of"), 4, "no tensors of its own"),
     (("layers", 3, "weights_of"), 0, "differ"),
-    (("layers", 2, "mixer", "softcap"), None, "lacks"),
+    (("layers", 2, "mixer", "scale"), None, "lacks"),
+    (("layers", 2, "mixer", "softcap"), -1.0, "positive"),
     (("norm", "eps"), 0, "positive"),
 ])
 def test_configuration_errors(path, value, text):
@@ -58,6 +59,16 @@ def test_plan_shares_tensors_and_not_caches():
     assert specs[2] == specs[4] == PagedKVSpec(2, 12, None, 8, 0, 7)
     assert specs[1] == specs[3] == FixedStateSpec((2 * 12 * 12 + 48,), torch.float32)
     assert plan.layers[1].ffn is None and plan.layers[1].ffn_norm is None
+
+
+def test_a_cap_or_a_mask_that_is_not_named_does_not_exist():
+    cfg = copy.deepcopy(SMALL_A)
+    for i in (2, 4):                      # (the two layers may share one dictionary)
+        cfg["layers"][i]["mixer"].pop("softcap", None)
+        cfg["layers"][i]["mixer"].pop("mask", None)
+    spec = _plan(cfg).layers[2].mixer
+    assert spec.params["softcap"] is None and spec.params["chunk"] is None
+    assert CausalLM(_plan(cfg)).cache_specs()[2] == PagedKVSpec(2, 12, None, 8, 0, None)
 
 
 def test_the_decay_width_is_the_stored_tensors():

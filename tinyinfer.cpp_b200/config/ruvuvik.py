@@ -59,9 +59,13 @@ def _mixer(entry, where: str, kind: str) -> dict:
         if heads % kv_heads:
             raise ConfigError(f"'{where}': {heads} heads cannot share {kv_heads} kv heads evenly")
         dims, base = _rotation(entry, where, dim)
+        # a constant that the configuration does not name does not exist: no cap, no chunks
+        m = entry["mixer"]
         return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": _int(entry, "mixer.vdim"),
-                "scale": _positive(entry, "mixer.scale"), "softcap": _positive(entry, "mixer.softcap"),
-                "chunk": _int(entry, "mixer.mask.size"), "rot_dims": dims, "rot_base": base}
+                "scale": _positive(entry, "mixer.scale"),
+                "softcap": None if m.get("softcap") is None else _positive(entry, "mixer.softcap"),
+                "chunk": None if m.get("mask") is None else _int(entry, "mixer.mask.size"),
+                "rot_dims": dims, "rot_base": base}
     if kind == "latent_attention":
         rot_dim = _int(entry, "mixer.rot_dim", 0)
         dims, base = _rotation(entry, where, rot_dim)
