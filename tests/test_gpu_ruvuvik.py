@@ -481,6 +481,33 @@ def test_random_weights_from_a_configuration(tmp_path):
     assert torch.isfinite(la).all() and torch.equal(la, lb)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_program(tmp_path_factory, tmp_path, dtype):
+    """The replay program as a user starts it: steps on standard input, logits in files."""
+    import json
+    import subprocess
+    import sys
+    import numpy as np
+    d = make_model(tmp_path_factory.getbasetemp(), "C")
+    steps = traces.mixed(_requests("C"), seed=9)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = str(tmp_path / "out")
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out", out,
+         "--max-tokens", str(traces.max_live_tokens(steps))],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [ln for ln in proc.stdout.splitlines() if ln.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    vocab = SMALL["C"][0]["vocab"]
+    outputs = {}
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        if wanted:
+            data = np.fromfile(os.path.join(out, f"{s['step']}.f32"), dtype="<f4")
+            outputs[s["step"]] = torch.from_numpy(data.reshape(wanted, vocab).copy())
+    _compare(steps, outputs, _plain(d, "C"), dtype, f"replay {dtype}")
+
+
 def test_command_line_with_token_ids(tmp_path_factory, capsys):
     from tinyinfer_b200 import cli
     d = make_model(tmp_path_factory.getbasetemp(), "B")
