@@ -271,25 +271,30 @@ def test_sink_and_shared_rows(ops, dtype):
     assert out.view(t, heads, dv)[:, 0].abs().max() < 1e-6          # the sink of 60 took everything
 
 
+@pytest.mark.parametrize("q_lens", [[1, 1, 1], [70, 2, 40]])
 @pytest.mark.parametrize("heads", [16, 24, 40])
-def test_shared_rows_of_single_tokens_with_many_heads(ops, heads):
-    """Single tokens over shared rows wide enough for several slices of value columns, with as many
-    heads as one block takes and more."""
+def test_wide_shared_rows_with_many_heads(ops, heads, q_lens):
+    """Single tokens and portions over shared rows wide enough for several slices of value columns,
+    with as many heads as one block takes and more."""
     dk, dv, ps = 288, 256, 16
     ctx = [70, 9, 300]
-    step, cache, bt, positions, req = _paged(ctx, [1, 1, 1], ps, dk, torch.bfloat16, seed=heads)
+    step, cache, bt, positions, req = _paged(ctx, q_lens, ps, dk, torch.bfloat16, seed=heads)
     g = torch.Generator().manual_seed(heads)
     rows = [torch.randn((c, 1, dk), generator=g) * 0.5 for c in ctx]
     _fill(cache, bt, rows, rows, 1, dk, 0)
-    q = torch.randn((3, heads, dk), generator=g) * 0.3
+    t = len(positions)
+    q = torch.randn((t, heads, dk), generator=g) * 0.3
     sink = torch.randn((heads,), generator=g)
-    out = torch.empty((3, heads * dv), dtype=torch.bfloat16, device=DEV)
-    ops.attention_options(q.reshape(3, -1).bfloat16().to(DEV), step, cache, out, heads, 1, dk, dv, 0.1,
+    out = torch.empty((t, heads * dv), dtype=torch.bfloat16, device=DEV)
+    ops.attention_options(q.reshape(t, -1).bfloat16().to(DEV), step, cache, out, heads, 1, dk, dv, 0.1,
                           sink=sink.to(DEV), shared_rows=True)
     rd = lambda x: x.bfloat16().double()
-    for r in range(3):
-        want = plain.attend(rd(q[r:r + 1]), rd(rows[r]), rd(rows[r])[:, :, :dv], [ctx[r] - 1], 0.1, sink=sink.double())
-        assert (out[r].cpu().double().view(1, heads, dv) - want).abs().max() < 2e-2
+    at = 0
+    for r, n in enumerate(q_lens):
+        want = plain.attend(rd(q[at:at + n]), rd(rows[r]), rd(rows[r])[:, :, :dv], positions[at:at + n], 0.1,
+                            sink=sink.double())
+        assert (out[at:at + n].cpu().double().view(n, heads, dv) - want).abs().max() < 2e-2
+        at += n
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

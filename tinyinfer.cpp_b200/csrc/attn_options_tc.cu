@@ -494,7 +494,9 @@ extern "C" int ti_attn_options_tc(const void* q, const int* tiles, int num_tiles
     int gp = ti_attn_options_tc_group_rows(num_heads, num_kv_heads);
     if (key_split == 2 && gp > 16) gp = 16;      // a tile is one token: more heads than 16 take several blocks
     const int group = num_heads / num_kv_heads, head_blocks = (group + gp - 1) / gp;
-    const int dvs = value_slice(dv);
+    // prompt portions over shared rows: 256 value columns a block where they divide, so that the score
+    // product of a wide row is repeated half as often (such a block fills an SM's shared memory anyway)
+    const int dvs = (shared_rows && key_split == 0 && dv % 256 == 0) ? 256 : value_slice(dv);
     const size_t smem = smem_bytes(dk, dv, shared_rows);
     TcOptions opt = {window, chunk, scale, softcap, head_scale, sink, gate, gate_stride, gate_per_head, shared_rows};
     TI_REQUIRE(key_split != 2 || (shared_rows && dv / dvs <= WARPS), "attn_options_tc: a warp per slice needs shared rows "
@@ -518,6 +520,7 @@ extern "C" int ti_attn_options_tc(const void* q, const int* tiles, int num_tiles
             part_ml, status);                                                                             \
     }
     switch (dvs) {
+        case 256: LAUNCH(256, 0) break;
         case 128: if (key_split == 2) LAUNCH(128, 2) else if (key_split) LAUNCH(128, 1) else LAUNCH(128, 0) break;
         case 64: if (key_split == 2) LAUNCH(64, 2) else if (key_split) LAUNCH(64, 1) else LAUNCH(64, 0) break;
         case 32: if (key_split == 2) LAUNCH(32, 2) else if (key_split) LAUNCH(32, 1) else LAUNCH(32, 0) break;

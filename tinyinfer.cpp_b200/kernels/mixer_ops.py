@@ -215,6 +215,8 @@ class MixerOps:
             # single tokens of few heads: the warps of a block share the rows and split the keys (1) or,
             # over shared rows, the slices of the value columns (2)
             mode = 0 if not single else 2 if (shared_rows and 1 < slices <= 4) else 1 if gp <= 16 else 0
+            if mode == 0 and shared_rows and dv % 256 == 0:
+                slices = dv // 256                    # prompt portions over shared rows: 256 columns a block
             head_blocks = -(-(num_heads // num_kv_heads) // (min(gp, 16) if mode == 2 else gp))
             blocks = tiles.shape[0] * num_kv_heads * head_blocks * (1 if mode == 2 else slices)
             if single and blocks < 2 * self.num_sms:
