@@ -298,16 +298,18 @@ def test_wide_shared_rows_with_many_heads(ops, heads, q_lens):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(3, 8, 20, 11), (1, 16, 16, 1), (4, 64, 96, 70), (2, 130, 12, 9)])
+@pytest.mark.parametrize("sizes", [(3, 8, 20, 11, 3), (1, 16, 16, 1, 3), (4, 64, 96, 70, 3), (2, 130, 12, 9, 3),
+                                   (3, 128, 512, 200, 8), (2, 80, 24, 130, 8), (16, 512, 128, 70, 8), (2, 48, 136, 65, 0)])
 def test_head_project(ops, sizes, dtype):
-    heads, n_in, n_out, t = sizes
+    """Few tokens, many tokens, and (bfloat16, rows that start on 16 bytes) many tokens on the tensor cores."""
+    heads, n_in, n_out, t, pad = sizes
     g = torch.Generator().manual_seed(n_in)
-    x = torch.randn((t, heads, n_in + 3), generator=g).to(dtype)
+    x = torch.randn((t, heads, n_in + pad), generator=g).to(dtype)
     w = torch.randn((heads, n_in, n_out), generator=g).to(torch.bfloat16)
     out = torch.zeros((t, heads, n_out + 5), dtype=dtype, device=DEV)
     ops.head_project(x.to(DEV)[:, :, :n_in], w.to(DEV), out[:, :, 2:2 + n_out])
     want = torch.einsum("thk,hkn->thn", x[:, :, :n_in].double(), w.double())
-    assert (out[:, :, 2:2 + n_out].cpu().double() - want).abs().max() < (2e-5 if dtype == torch.float32 else 0.15)
+    assert (out[:, :, 2:2 + n_out].cpu().double() - want).abs().max() < (2e-5 * n_in ** 0.5 if dtype == torch.float32 else 0.3)
     assert out[:, :, :2].abs().max() == 0 and out[:, :, 2 + n_out:].abs().max() == 0
 
 

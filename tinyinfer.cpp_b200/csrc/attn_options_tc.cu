@@ -445,6 +445,81 @@ attn_options_merge_kernel(const float* part_o, const float* part_ml, int nsplit,
     }
 }
 
+// out[t, h, :] = x[t, h, :] W[h] on the tensor cores, for many tokens: a block has 64 tokens of one head and
+// 128 columns; the tokens' rows lie in shared memory, W[h] ([n_in, n_out], columns contiguous) comes in runs
+// of 64 of its rows through a two-stage cp.async ring and is read transposed, as the values of the attention
+// kernel are.
+constexpr int HPK = 64;          // rows of W[h] a stage holds
+constexpr int HP_WROW = 128 * 2 + 16;
+
+__global__ void __launch_bounds__(WARPS * 32)
+head_project_tc_kernel(const bf16* x, int x_stride_t, int x_stride_h, const bf16* __restrict__ w, int n_in, int n_out,
+                       bf16* out, int out_stride_t, int out_stride_h, int num_tokens) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int x_row = n_in * 2 + 16;
+    unsigned char* xs = smem;
+    unsigned char* ring = smem + (size_t)BM * x_row;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+    const int t0 = blockIdx.x * BM, h = blockIdx.y, n0 = blockIdx.z * 128;
+    const int chunks = n_in / 8;
+    for (int c = threadIdx.x; c < BM * chunks; c += WARPS * 32) {
+        const int i = c / chunks, part = c % chunks;
+        const bool ok = t0 + i < num_tokens;
+        cp_async16(xs + (size_t)i * x_row + part * 16,
+                   x + (ok ? (size_t)(t0 + i) * x_stride_t + (size_t)h * x_stride_h + part * 8 : 0), ok);
+    }
+    const bf16* wh = w + (size_t)h * n_in * n_out;
+    auto issue = [&](int kc, int stage) {
+        unsigned char* dst = ring + (size_t)stage * HPK * HP_WROW;
+        for (int c = threadIdx.x; c < HPK * 16; c += WARPS * 32) {
+            const int k = kc * HPK + c / 16, col = n0 + (c % 16) * 8;
+            const bool ok = k < n_in && col < n_out;
+            cp_async16(dst + (size_t)(c / 16) * HP_WROW + (c % 16) * 16, wh + (ok ? (size_t)k * n_out + col : 0), ok);
+        }
+    };
+    float o[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    const int num_kc = (n_in + HPK - 1) / HPK;
+    issue(0, 0);
+    cp_async_commit();
+    for (int kc = 0; kc < num_kc; ++kc) {
+        if (kc + 1 < num_kc) issue(kc + 1, (kc + 1) % STAGES);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const unsigned char* ws = ring + (size_t)(kc % STAGES) * HPK * HP_WROW;
+        const int steps = min(HPK, n_in - kc * HPK) / 16;
+        for (int ks = 0; ks < steps; ++ks) {
+            unsigned a[4];
+            ldmatrix_x4(a, xs + (size_t)(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * x_row
+                               + (kc * HPK + ks * 16 + (lane >> 4) * 8) * 2);
+#pragma unroll
+            for (int dp = 0; dp < 8; ++dp) {
+                unsigned b[4];
+                const int k = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                ldmatrix_x4_trans(b, ws + (size_t)k * HP_WROW + (dp * 16 + (lane >> 4) * 8) * 2);
+                mma_bf16(o[2 * dp], a, b[0], b[1]);
+                mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int t = t0 + warp * 16 + g + 8 * r;
+        if (t >= num_tokens) continue;
+        bf16* dst = out + (size_t)t * out_stride_t + (size_t)h * out_stride_h + n0 + tq * 2;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int col = n0 + i * 8 + tq * 2;
+            if (col < n_out) dst[i * 8] = __float2bfloat16_rn(o[i][2 * r]);
+            if (col + 1 < n_out) dst[i * 8 + 1] = __float2bfloat16_rn(o[i][2 * r + 1]);
+        }
+    }
+}
+
 int value_slice(int dv) { return dv % 128 == 0 ? 128 : dv % 64 == 0 ? 64 : dv % 32 == 0 ? 32 : 16; }
 
 size_t smem_bytes(int dk, int dv, int shared_rows) {
@@ -459,6 +534,35 @@ size_t smem_bytes(int dk, int dv, int shared_rows) {
 extern "C" int ti_attn_options_tc_supported(int dk, int dv, int page_size, int shared_rows) {
     return dk >= 16 && dk % 16 == 0 && dv >= 16 && dv % 16 == 0 && page_size >= 16 && page_size % 16 == 0 &&
            (!shared_rows || dv <= dk) && smem_bytes(dk, dv, shared_rows) <= 227 * 1024;
+}
+
+extern "C" int ti_head_project_tc_supported(int n_in, int n_out, int x_stride_t, int x_stride_h) {
+    return n_in >= 16 && n_in % 16 == 0 && n_out % 8 == 0 && x_stride_t % 8 == 0 && x_stride_h % 8 == 0 &&
+           (size_t)BM * (n_in * 2 + 16) + (size_t)STAGES * HPK * HP_WROW <= 227 * 1024;
+}
+
+// x: bfloat16 [T, heads, n_in] (strides over tokens and heads, 16-byte aligned rows), w: bfloat16 [heads, n_in, n_out],
+// out: bfloat16 [T, heads, n_out] (strides over tokens and heads)
+extern "C" int ti_head_project_tc(const void* x, int x_stride_t, int x_stride_h, const void* w, int n_in, int n_out,
+                                  void* out, int out_stride_t, int out_stride_h, int num_tokens, int num_heads,
+                                  void* stream) {
+    if (num_tokens == 0 || num_heads == 0) return 0;
+    TI_REQUIRE(ti_head_project_tc_supported(n_in, n_out, x_stride_t, x_stride_h) && (uintptr_t)x % 16 == 0 &&
+               (uintptr_t)w % 16 == 0, "head_project_tc: sizes %d x %d, strides %d, %d or alignment are not supported",
+               n_in, n_out, x_stride_t, x_stride_h);
+    const size_t smem = (size_t)BM * (n_in * 2 + 16) + (size_t)STAGES * HPK * HP_WROW;
+    static TiPerDevice configured;
+    if (configured.first_use()) {
+        cudaError_t e = cudaFuncSetAttribute(head_project_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             227 * 1024);
+        if (e != cudaSuccess) return ti_fail("head_project_tc: %s", cudaGetErrorString(e));
+        configured.mark();
+    }
+    dim3 grid((num_tokens + BM - 1) / BM, num_heads, (n_out + 127) / 128);
+    head_project_tc_kernel<<<grid, WARPS * 32, smem, (cudaStream_t)stream>>>(
+        (const bf16*)x, x_stride_t, x_stride_h, (const bf16*)w, n_in, n_out, (bf16*)out, out_stride_t, out_stride_h,
+        num_tokens);
+    return ti_check_launch("head_project_tc");
 }
 
 // rows of a block that belong to one token: the heads of a kv group, padded to a power of two (at most 64)

@@ -64,6 +64,8 @@ class MixerOps:
             b.ti_last_error.restype = ctypes.c_char_p
             b.ti_attn_options_tc_supported.argtypes = [_i, _i, _i, _i]
             b.ti_attn_options_tc_group_rows.argtypes = [_i, _i]
+            b.ti_head_project_tc_supported.argtypes = [_i, _i, _i, _i]
+            b.ti_head_project_tc.argtypes = [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _i, _i, _vp]
             b.ti_attn_options_tc.argtypes = [_vp, _vp, _i, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i,
                                              _f, _f, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp]
             self._mixers_tc = b
@@ -172,6 +174,13 @@ class MixerOps:
                    and tuple(out.shape) == (t, heads, n_out), "head_project: shapes do not agree")
         self._must(x.stride(2) == 1 and out.stride(2) == 1 and x.dtype == out.dtype,
                    "head_project: contiguous last axes and one dtype for input and output")
+        if (t > 64 and x.dtype == w.dtype == torch.bfloat16 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+                and self.mixers_tc.ti_head_project_tc_supported(n_in, n_out, x.stride(0), x.stride(1))):
+            # many tokens: on the tensor cores
+            self._ok(self.mixers_tc.ti_head_project_tc(
+                x.data_ptr(), x.stride(0), x.stride(1), w.data_ptr(), n_in, n_out, out.data_ptr(), out.stride(0),
+                out.stride(1), t, heads, self._stream()), self.mixers_tc)
+            return
         self._mx(self.mixers.ti_head_project(
             x.data_ptr(), _CODE[x.dtype], x.stride(0), x.stride(1), w.data_ptr(), _CODE[w.dtype], n_in, n_out,
             out.data_ptr(), _CODE[out.dtype], out.stride(0), out.stride(1), t, heads, self._stream()))
