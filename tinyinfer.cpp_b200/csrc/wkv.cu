@@ -44,8 +44,8 @@ token_shift_mix_kernel(const TH* h, const float* __restrict__ mu, int n_mix, int
 // Tokens are staged a tile (16 or 8) at a time: cp.async brings the tile's r, k, v, g and decay arguments
 // into one of two buffers in shared memory while the tile before is worked on, then
 // the tile's tokens follow one another without a barrier: column j of the state belongs to four
-// neighbouring lanes, each holding a quarter of its rows (read four at a time); the four partial sums
-// of o_j meet through two shuffles.  The unit norm of the tile's rows is taken afterwards, a warp per
+// neighbouring lanes (sixteen in the column-split form), each holding its share of the rows (read four
+// at a time); their partial sums of o_j meet through shuffles once per tile.  The unit norm of the tile's rows is taken afterwards, a warp per
 // token.  JS > 1 (long portions of few requests): a head's columns are cut over JS blocks, each with
 // the whole of r, k and the decays and its own columns of v; the blocks write o as float32 and a
 // second launch (wkv_finish) takes the norm, the weight and the gate.
@@ -133,28 +133,43 @@ wkv_recurrence_kernel(const float* r, const float* k, const float* v, const floa
         }
         __syncthreads();
         const int nt = min(WKV_TT, t1 - tile0);
-        for (int tt = 0; tt < nt; ++tt) {
-            const float vj = vs[buf][tt][j - c0];
-            float o = 0.0f;
-            const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][part * 4]);
-            const float4* r4 = reinterpret_cast<const float4*>(&rs[buf][tt][part * 4]);
-            const float4* w4 = reinterpret_cast<const float4*>(&ws[tt][part * 4]);
+        // every lane keeps its part of o for each token of the tile; the lanes of a column meet once
+        // per tile, sixteen independent exchanges in flight, instead of once per token
+        float o_part[WKV_TT];
 #pragma unroll
-            for (int q4 = 0; q4 < NI / 4; ++q4) {        // four rows a load
-                const float4 kq = k4[q4 * WKV_IS], rq = r4[q4 * WKV_IS], wq = w4[q4 * WKV_IS];
-                const float kk[4] = {kq.x, kq.y, kq.z, kq.w}, rr[4] = {rq.x, rq.y, rq.z, rq.w};
-                const float ww[4] = {wq.x, wq.y, wq.z, wq.w};
+        for (int tt = 0; tt < WKV_TT; ++tt) {
+            o_part[tt] = 0.0f;
+            if (tt < nt) {
+                const float vj = vs[buf][tt][j - c0];
+                float o = 0.0f;
+                const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][part * 4]);
+                const float4* r4 = reinterpret_cast<const float4*>(&rs[buf][tt][part * 4]);
+                const float4* w4 = reinterpret_cast<const float4*>(&ws[tt][part * 4]);
 #pragma unroll
-                for (int x = 0; x < 4; ++x) {
-                    const int ii = q4 * 4 + x;
-                    const float kv = kk[x] * vj;
-                    o = fmaf(rr[x], fmaf(ur[ii], kv, S[ii]), o);
-                    S[ii] = fmaf(ww[x], S[ii], kv);
+                for (int q4 = 0; q4 < NI / 4; ++q4) {        // four rows a load
+                    const float4 kq = k4[q4 * WKV_IS], rq = r4[q4 * WKV_IS], wq = w4[q4 * WKV_IS];
+                    const float kk[4] = {kq.x, kq.y, kq.z, kq.w}, rr[4] = {rq.x, rq.y, rq.z, rq.w};
+                    const float ww[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        const int ii = q4 * 4 + x;
+                        const float kv = kk[x] * vj;
+                        o = fmaf(rr[x], fmaf(ur[ii], kv, S[ii]), o);
+                        S[ii] = fmaf(ww[x], S[ii], kv);
+                    }
                 }
+                o_part[tt] = o;
             }
+        }
 #pragma unroll
-            for (int sh = 1; sh < WKV_IS; sh *= 2) o += __shfl_xor_sync(0xffffffffu, o, sh);
-            if (part == 0) os[tt][j - c0] = live ? o : 0.0f;
+        for (int sh = 1; sh < WKV_IS; sh *= 2) {
+#pragma unroll
+            for (int tt = 0; tt < WKV_TT; ++tt) o_part[tt] += __shfl_xor_sync(0xffffffffu, o_part[tt], sh);
+        }
+        if (part == 0) {
+#pragma unroll
+            for (int tt = 0; tt < WKV_TT; ++tt)
+                if (tt < nt) os[tt][j - c0] = live ? o_part[tt] : 0.0f;
         }
         __syncthreads();
         if (JS > 1) {                                    // the row's other columns are elsewhere

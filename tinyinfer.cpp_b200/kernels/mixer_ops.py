@@ -211,7 +211,7 @@ class MixerOps:
                    "attention_options: the gate must be float32 [T, heads] or [T, heads * dv]")
         gp = self._group_rows(num_heads, num_kv_heads)
         tiles = getattr(step, "lists", {}).get(f"row_tiles_{64 // gp}")
-        if (self.use_tc_attention_options and tiles is not None and q.dtype == torch.bfloat16
+        if (self.use_tc_attention_options and tiles is not None and 0 < tiles.shape[0] <= 65535 and q.dtype == torch.bfloat16
                 and pages.dtype == torch.bfloat16 and q.data_ptr() % 16 == 0 and out.data_ptr() % 4 == 0
                 and pages.data_ptr() % 16 == 0
                 and self.mixers_tc.ti_attn_options_tc_supported(dk, dv, cache.page_size, int(bool(shared_rows)))
