@@ -579,10 +579,10 @@ def ruvuvik_config(size):
     layers = [
         {"type": "attention", "mlp": mlp,
          "mixer": {"heads": h, "kv_heads": g, "dim": d, "vdim": d, "mask": {"size": chunk},
-                   "rot": {"dims": d, "base": 500000.0}, "scale": d ** -0.5, "softcap": 30.0}},
+                   "rot": {"dims": d, "base": 10000.0}, "scale": d ** -0.5, "softcap": 50.0}},
         {"type": "latent_attention", "mlp": mlp,
          "mixer": {"heads": h, "dim": d, "rot_dim": dr, "vdim": d, "kv_rank": rank,
-                   "rot": {"dims": dr, "base": 1000000.0}, "scale": (d + dr) ** -0.5}},
+                   "rot": {"dims": dr, "base": 100000.0}, "scale": (d + dr) ** -0.5}},
         {"type": "wkv", "mlp": mlp, "mixer": {"heads": w // rd, "dim": rd, "decay_rank": 64}}]
     return {"architecture": "Ruvuvik", "vocab": DESIGN_VOCAB, "width": w, "norm": {"eps": 1e-5},
             "layers": layers * blocks}
